@@ -1,0 +1,117 @@
+// extern "C" surface of libdscuda_mla_bench.so.  Same symbols and signatures as
+// the reference's benchmarks/bindings/mla_bridge.cu:12-73, plus the prefill
+// entry points.  C++ exceptions stop here: they become status 1 and a
+// thread-local message.
+#include "mla.h"
+
+#include <exception>
+#include <string>
+
+namespace {
+thread_local std::string last_error;
+
+template <class Call>
+int guarded(Call&& call) {
+    try {
+        call();
+        return 0;
+    } catch (const std::exception& error) {
+        last_error = error.what();
+        return 1;
+    } catch (...) {
+        last_error = "unknown failure";
+        return 1;
+    }
+}
+}  // namespace
+
+using bf16 = __nv_bfloat16;
+
+extern "C" const char* dscuda_mla_last_error() {
+    return last_error.c_str();
+}
+
+extern "C" int dscuda_mla_forward(bf16* output, float* lse, const bf16* query, const bf16* query_rope, const bf16* latent,
+                                  const bf16* key_rope, int batch, int sequence, int heads, int rank, int rope, float scale,
+                                  cudaStream_t stream) {
+    return guarded([&] {
+        dscuda::mla_compressed_attention_forward_cuda(output, lse, query, query_rope, latent, key_rope, batch, sequence, heads,
+                                                      rank, rope, scale, stream);
+    });
+}
+
+extern "C" int dscuda_mla_backward(bf16* dquery, bf16* dquery_rope, bf16* dlatent, bf16* dkey_rope, const bf16* dout,
+                                   const bf16* output, const float* lse, const bf16* query, const bf16* query_rope,
+                                   const bf16* latent, const bf16* key_rope, int batch, int sequence, int heads, int rank,
+                                   int rope, float scale, cudaStream_t stream) {
+    return guarded([&] {
+        dscuda::mla_compressed_attention_backward_cuda(dquery, dquery_rope, dlatent, dkey_rope, dout, output, lse, query,
+                                                       query_rope, latent, key_rope, batch, sequence, heads, rank, rope, scale,
+                                                       stream);
+    });
+}
+
+extern "C" std::size_t dscuda_mla_workspace_elements(int batch, int heads, int splits, int rank) {
+    return dscuda::mla_decode_workspace_elements(batch, heads, splits, rank);
+}
+
+extern "C" int dscuda_mla_decode(bf16* output, float* lse, const bf16* query, const bf16* paged_cache, const int* block_table,
+                                 const int* lengths, float* workspace, int batch, int heads, int rank, int rope, int page_size,
+                                 int pages, int splits, float scale, cudaStream_t stream) {
+    return guarded([&] {
+        dscuda::mla_decode_forward_cuda(output, lse, query, paged_cache, block_table, lengths, workspace, batch, heads, rank, rope,
+                                        page_size, pages, splits, scale, stream);
+    });
+}
+
+extern "C" int dscuda_mla_prefill_forward(bf16* output, float* lse, const bf16* q_nope, const bf16* q_pe, const bf16* k_nope,
+                                          const bf16* k_pe, const bf16* v, const int* cu_seqlens, int batch, int max_sequence,
+                                          int total_tokens, int heads, int nope, int rope, int value, float scale,
+                                          cudaStream_t stream) {
+    return guarded([&] {
+        dscuda::mla_prefill_forward_cuda(output, lse, q_nope, q_pe, k_nope, k_pe, v, cu_seqlens, batch, max_sequence, total_tokens,
+                                         heads, nope, rope, value, scale, stream);
+    });
+}
+
+extern "C" std::size_t dscuda_mla_prefill_backward_workspace_bytes(int batch, int max_sequence, int total_tokens, int heads) {
+    return dscuda::mla_prefill_backward_workspace_bytes(batch, max_sequence, total_tokens, heads);
+}
+
+extern "C" int dscuda_mla_prefill_backward(bf16* dq, bf16* dk_nope, bf16* dk_pe, bf16* dv, const bf16* dout, const bf16* output,
+                                           const float* lse, const bf16* q_nope, const bf16* q_pe, const bf16* k_nope,
+                                           const bf16* k_pe, const bf16* v, const int* cu_seqlens, void* workspace, int batch,
+                                           int max_sequence, int total_tokens, int heads, int nope, int rope, int value,
+                                           float scale, cudaStream_t stream) {
+    return guarded([&] {
+        dscuda::mla_prefill_backward_cuda(dq, dk_nope, dk_pe, dv, dout, output, lse, q_nope, q_pe, k_nope, k_pe, v, cu_seqlens,
+                                          workspace, batch, max_sequence, total_tokens, heads, nope, rope, value, scale, stream);
+    });
+}
+
+extern "C" int dscuda_mla_device_status(int reset) {
+    int status = -1;
+    if (guarded([&] { status = dscuda::mla_device_status(reset != 0); }) != 0) {
+        return -1;
+    }
+    return status;
+}
+
+#ifdef DSCUDA_DEBUG_DUMP
+// Diagnostic builds only: raw score / accumulator dumps of the first CTA.
+#include "../attention/attention_internal.h"
+namespace dscuda { namespace internal { extern float* absorbed_debug_buffer; } }
+
+extern "C" int dscuda_debug_prefill_forward(bf16* output, float* lse, const bf16* q_nope, const bf16* q_pe, const bf16* k_nope,
+                                            const bf16* k_pe, const bf16* v, const int* cu_seqlens, int batch, int max_sequence,
+                                            int total_tokens, int heads, float scale, float* debug, cudaStream_t stream) {
+    return guarded([&] {
+        dscuda::internal::launch_prefill_forward(output, lse, q_nope, q_pe, k_nope, k_pe, v, cu_seqlens, batch, max_sequence,
+                                                 total_tokens, heads, scale, debug, stream);
+    });
+}
+
+extern "C" void dscuda_debug_set_absorbed_buffer(float* debug) {
+    dscuda::internal::absorbed_debug_buffer = debug;
+}
+#endif

@@ -1,0 +1,19 @@
+// Host-side construction of TMA tensor maps for 2-D bf16 views with 128-byte
+// swizzle.  The driver entry point is looked up at run time, so the library
+// does not link against libcuda.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace dscuda {
+
+// View of `rows` x `cols` bf16 elements whose rows are `row_stride_elements`
+// apart; the box is `box_rows` x 64 elements (128 bytes wide), swizzled.
+// Out-of-range elements are read as zero.  Throws on bad alignment.
+CUtensorMap make_bf16_tile_map(const void* base, std::uint64_t rows, std::uint64_t cols, std::uint64_t row_stride_elements,
+                               std::uint32_t box_rows);
+
+}  // namespace dscuda

@@ -1,0 +1,161 @@
+"""Host side of the MLA path: torch tensors in, C-ABI calls out.
+
+The functions mirror what the reference's `benchmarks/mla.py:79-117` does by
+hand (raw `data_ptr()`s, the current stream, caller-owned outputs and
+workspace).  They allocate outputs with torch, launch on the current stream and
+return without synchronising.  Inputs must be contiguous CUDA tensors; bf16
+unless stated.  No CPU fallback exists.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .library import checked, library  # noqa: F401 (re-exported for callers)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(tensor):
+    return None if tensor is None else tensor.data_ptr()
+
+
+def _require(*tensors):
+    for tensor in tensors:
+        if tensor is None:
+            continue
+        if not tensor.is_cuda:
+            raise RuntimeError("dscuda_b200 runs on CUDA tensors only; there is no CPU path")
+        if not tensor.is_contiguous():
+            raise ValueError("tensors must be contiguous")
+
+
+def mla_forward(query, query_rope, latent, key_rope, scale):
+    """Absorbed causal forward (`dscuda_mla_forward`).
+    query [B,T,H,512], query_rope [B,T,H,64], latent [B,T,512], key_rope [B,T,64]
+    -> (output [B,T,H,512] bf16, lse [B,H,T] fp32)."""
+    _require(query, query_rope, latent, key_rope)
+    b, t, h, c = query.shape
+    r = query_rope.shape[-1]
+    output = torch.empty_like(query)
+    lse = torch.empty(b, h, t, device=query.device, dtype=torch.float32)
+    lib = library("mla")
+    checked(lib, "mla", lib.dscuda_mla_forward(
+        _ptr(output), _ptr(lse), _ptr(query), _ptr(query_rope), _ptr(latent), _ptr(key_rope),
+        b, t, h, c, r, scale, _stream()))
+    return output, lse
+
+
+def mla_backward(dout, output, lse, query, query_rope, latent, key_rope, scale):
+    """Absorbed backward (`dscuda_mla_backward`) -> (dquery, dquery_rope, dlatent, dkey_rope)."""
+    _require(dout, output, lse, query, query_rope, latent, key_rope)
+    b, t, h, c = query.shape
+    r = query_rope.shape[-1]
+    grads = tuple(torch.empty_like(x) for x in (query, query_rope, latent, key_rope))
+    lib = library("mla")
+    checked(lib, "mla", lib.dscuda_mla_backward(
+        *map(_ptr, grads), _ptr(dout), _ptr(output), _ptr(lse), _ptr(query), _ptr(query_rope), _ptr(latent), _ptr(key_rope),
+        b, t, h, c, r, scale, _stream()))
+    return grads
+
+
+def decode_workspace(batch, heads, splits, rank=512, device="cuda"):
+    lib = library("mla")
+    return torch.empty(lib.dscuda_mla_workspace_elements(batch, heads, splits, rank), device=device, dtype=torch.float32)
+
+
+def mla_decode(query, paged_cache, block_table, lengths, scale, splits=8, workspace=None, output=None, lse=None):
+    """Paged decode (`dscuda_mla_decode`).
+    query [B,1,H,576], paged_cache [blocks,page,1,576], block_table [B,pages] int32,
+    lengths [B] int32 -> (output [B,1,H,512] bf16, lse [B,H,1] fp32)."""
+    _require(query, paged_cache, block_table, lengths, workspace)
+    b, _, h, width = query.shape
+    rank, rope = 512, width - 512
+    page_size = paged_cache.shape[1]
+    if workspace is None:
+        workspace = decode_workspace(b, h, splits, rank, query.device)
+    if output is None:
+        output = torch.empty(b, 1, h, rank, device=query.device, dtype=torch.bfloat16)
+    if lse is None:
+        lse = torch.empty(b, h, 1, device=query.device, dtype=torch.float32)
+    lib = library("mla")
+    checked(lib, "mla", lib.dscuda_mla_decode(
+        _ptr(output), _ptr(lse), _ptr(query), _ptr(paged_cache), _ptr(block_table), _ptr(lengths), _ptr(workspace),
+        b, h, rank, rope, page_size, block_table.shape[1], splits, scale, _stream()))
+    return output, lse
+
+
+def _prefill_dims(q_nope, cu_seqlens, max_seqlen):
+    if cu_seqlens is None:
+        b, s, h, _ = q_nope.shape
+        return b, s, b * s, h
+    total, h, _ = q_nope.shape
+    if max_seqlen is None:
+        raise ValueError("packed layout needs max_seqlen (an upper bound on the longest sequence)")
+    return cu_seqlens.numel() - 1, int(max_seqlen), total, h
+
+
+def prefill_forward(q_nope, q_pe, k_nope, k_pe, v, scale, cu_seqlens=None, max_seqlen=None, output=None, lse=None):
+    """Non-absorbed causal forward (`dscuda_mla_prefill_forward`).
+    Dense [B,S,H,*] or packed [total,H,*] with int32 cu_seqlens on the device.
+    -> (output like v, lse [B,H,S] or [H,total])."""
+    _require(q_nope, q_pe, k_nope, k_pe, v, cu_seqlens)
+    batch, max_seq, total, heads = _prefill_dims(q_nope, cu_seqlens, max_seqlen)
+    if output is None:
+        output = torch.empty_like(v)
+    if lse is None:
+        shape = (batch, heads, max_seq) if cu_seqlens is None else (heads, total)
+        lse = torch.empty(shape, device=v.device, dtype=torch.float32)
+    lib = library("mla")
+    checked(lib, "mla", lib.dscuda_mla_prefill_forward(
+        _ptr(output), _ptr(lse), _ptr(q_nope), _ptr(q_pe), _ptr(k_nope), _ptr(k_pe), _ptr(v), _ptr(cu_seqlens),
+        batch, max_seq, total, heads, q_nope.shape[-1], q_pe.shape[-1], v.shape[-1], scale, _stream()))
+    return output, lse
+
+
+def prefill_backward_workspace(batch, max_seq, total, heads, device="cuda"):
+    lib = library("mla")
+    return torch.empty(lib.dscuda_mla_prefill_backward_workspace_bytes(batch, max_seq, total, heads),
+                       device=device, dtype=torch.uint8)
+
+
+def prefill_backward(dout, output, lse, q_nope, q_pe, k_nope, k_pe, v, scale, cu_seqlens=None, max_seqlen=None,
+                     workspace=None, grads=None):
+    """Non-absorbed backward (`dscuda_mla_prefill_backward`)
+    -> (dq [...,H,192], dk_nope [...,H,128], dk_pe [...,1,64], dv [...,H,128])."""
+    _require(dout, output, lse, q_nope, q_pe, k_nope, k_pe, v, cu_seqlens, workspace)
+    batch, max_seq, total, heads = _prefill_dims(q_nope, cu_seqlens, max_seqlen)
+    if workspace is None:
+        workspace = prefill_backward_workspace(batch, max_seq, total, heads, v.device)
+    if grads is None:
+        lead = q_nope.shape[:-1]
+        dq = torch.empty(*lead, 192, device=v.device, dtype=torch.bfloat16)
+        grads = (dq, torch.empty_like(k_nope), torch.empty_like(k_pe), torch.empty_like(v))
+    lib = library("mla")
+    checked(lib, "mla", lib.dscuda_mla_prefill_backward(
+        *map(_ptr, grads), _ptr(dout), _ptr(output), _ptr(lse), _ptr(q_nope), _ptr(q_pe), _ptr(k_nope), _ptr(k_pe), _ptr(v),
+        _ptr(cu_seqlens), _ptr(workspace), batch, max_seq, total, heads,
+        q_nope.shape[-1], q_pe.shape[-1], v.shape[-1], scale, _stream()))
+    return grads
+
+
+def flash_forward(query, key, value, scale):
+    """Causal D=128 GQA forward (`dscuda_flash_forward`).
+    query [B,T,Hq,128], key/value [B,T,Hkv,128] -> (output, lse [B,Hq,T])."""
+    _require(query, key, value)
+    b, t, hq, d = query.shape
+    output = torch.empty_like(query)
+    lse = torch.empty(b, hq, t, device=query.device, dtype=torch.float32)
+    lib = library("flash_attention")
+    checked(lib, "flash", lib.dscuda_flash_forward(
+        _ptr(output), _ptr(lse), _ptr(query), _ptr(key), _ptr(value), b, t, hq, key.shape[2], d, scale, _stream()))
+    return output, lse
+
+
+def device_status(reset=False) -> int:
+    """0 when no kernel of this library has hit a bounded-wait timeout."""
+    mla = library("mla").dscuda_mla_device_status(int(reset))
+    flash = library("flash_attention").dscuda_flash_device_status(int(reset))
+    return mla or flash

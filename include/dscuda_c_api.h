@@ -1,0 +1,96 @@
+/* C ABI of libdscuda_mla_bench.so and libdscuda_flash_attention_bench.so.
+ *
+ * Plain pointers and sizes only.  Every tensor argument is a DEVICE pointer the
+ * caller owns; `stream` is a cudaStream_t passed as void*.  Functions returning
+ * int give 0 on success and 1 on failure; the message of the last failure on the
+ * calling thread is returned by the matching *_last_error().  No call
+ * allocates, synchronises or reads device memory back, so all of them can be
+ * captured in a CUDA graph.
+ *
+ * The symbols marked "reference:" replace the extern "C" function of the same
+ * name in the reference's benchmarks/bindings/ and keep its signature, so the
+ * reference's benchmarks/mla.py and benchmarks/flash_attention.py bind them
+ * unchanged.
+ */
+#ifndef DSCUDA_C_API_H
+#define DSCUDA_C_API_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* reference: benchmarks/bindings/mla_bridge.cu:12 */
+const char* dscuda_mla_last_error(void);
+
+/* reference: benchmarks/bindings/mla_bridge.cu:16-21 (ctypes [P]*6+[I]*5+[F,P],
+ * benchmarks/mla.py:28).  Absorbed causal forward; bf16 tensors, fp32 lse. */
+int dscuda_mla_forward(
+    void* output, float* lse,
+    const void* query, const void* query_rope, const void* latent, const void* key_rope,
+    int batch, int sequence, int heads, int rank, int rope, float scale, void* stream);
+
+/* reference: benchmarks/bindings/mla_bridge.cu:33-40 ([P]*11+[I]*5+[F,P],
+ * benchmarks/mla.py:29). */
+int dscuda_mla_backward(
+    void* dquery, void* dquery_rope, void* dlatent, void* dkey_rope,
+    const void* dout, const void* output, const float* lse,
+    const void* query, const void* query_rope, const void* latent, const void* key_rope,
+    int batch, int sequence, int heads, int rank, int rope, float scale, void* stream);
+
+/* reference: benchmarks/bindings/mla_bridge.cu:53-56 (benchmarks/mla.py:31-32). */
+size_t dscuda_mla_workspace_elements(int batch, int heads, int splits, int rank);
+
+/* reference: benchmarks/bindings/mla_bridge.cu:58-63 ([P]*7+[I]*7+[F,P],
+ * benchmarks/mla.py:30). */
+int dscuda_mla_decode(
+    void* output, float* lse,
+    const void* query, const void* paged_cache,
+    const int* block_table, const int* lengths, float* workspace,
+    int batch, int heads, int rank, int rope, int page_size, int pages, int splits,
+    float scale, void* stream);
+
+/* No counterpart in the reference: non-absorbed causal prefill forward
+ * (include/mla.h, mla_prefill_forward_cuda).  cu_seqlens may be NULL (dense). */
+int dscuda_mla_prefill_forward(
+    void* output, float* lse,
+    const void* q_nope, const void* q_pe, const void* k_nope, const void* k_pe, const void* v,
+    const int* cu_seqlens, int batch, int max_sequence, int total_tokens, int heads,
+    int nope, int rope, int value, float scale, void* stream);
+
+/* No counterpart in the reference (mla_prefill_backward_workspace_bytes). */
+size_t dscuda_mla_prefill_backward_workspace_bytes(
+    int batch, int max_sequence, int total_tokens, int heads);
+
+/* No counterpart in the reference (mla_prefill_backward_cuda). */
+int dscuda_mla_prefill_backward(
+    void* dq, void* dk_nope, void* dk_pe, void* dv,
+    const void* dout, const void* output, const float* lse,
+    const void* q_nope, const void* q_pe, const void* k_nope, const void* k_pe, const void* v,
+    const int* cu_seqlens, void* workspace,
+    int batch, int max_sequence, int total_tokens, int heads,
+    int nope, int rope, int value, float scale, void* stream);
+
+/* No counterpart in the reference: sticky device status of the MLA kernels
+ * (0 fine, 1 a bounded in-kernel wait ran out).  Synchronises the device. */
+int dscuda_mla_device_status(int reset);
+
+/* reference: benchmarks/bindings/flash_attention_bridge.cu:13 */
+const char* dscuda_flash_last_error(void);
+
+/* reference: benchmarks/bindings/flash_attention_bridge.cu:17-20 ([P]*5+[I]*5+[F,P],
+ * benchmarks/flash_attention.py:37). */
+int dscuda_flash_forward(
+    void* output, float* lse, const void* query, const void* key, const void* value,
+    int batch, int sequence, int query_heads, int key_value_heads, int dimension,
+    float scale, void* stream);
+
+/* No counterpart in the reference: device status of the flash kernel. */
+int dscuda_flash_device_status(int reset);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* DSCUDA_C_API_H */

@@ -1,0 +1,177 @@
+// Multi-head Latent Attention host API.
+//
+// The first four functions are drop-ins for the reference's include/mla.h
+// (forward :18, backward :35, workspace size :57, paged decode :65): same names,
+// argument order, layouts and error behaviour.  The prefill functions below
+// them have no counterpart in the reference; they cover the non-absorbed form
+// (per-head k_nope / v, one shared k_pe head) in dense and packed layouts.
+//
+// Every function only launches work on `stream`: no allocation, no
+// synchronisation, no host read-back, so a call can be captured in a CUDA
+// graph.  Bad arguments throw std::invalid_argument, CUDA failures throw
+// std::runtime_error (as the reference's CUDA_CHECK does).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+
+namespace dscuda {
+
+constexpr int MLA_KV_RANK = 512;
+constexpr int MLA_ROPE_SIZE = 64;
+constexpr int MLA_NOPE_SIZE = 128;
+constexpr int MLA_VALUE_SIZE = 128;
+
+// Absorbed-query causal forward.  query_latent [B,T,H,C], query_rope [B,T,H,R],
+// kv_latent [B,T,C] and key_rope [B,T,R] shared by all heads, output [B,T,H,C],
+// logsumexp [B,H,T] (natural log, scale included).  C=512, R=64 only; B, T, H
+// are free.
+void mla_compressed_attention_forward_cuda(
+    __nv_bfloat16* output,
+    float* logsumexp,
+    const __nv_bfloat16* query_latent,
+    const __nv_bfloat16* query_rope,
+    const __nv_bfloat16* kv_latent,
+    const __nv_bfloat16* key_rope,
+    int batch_size,
+    int sequence_length,
+    int heads,
+    int kv_rank,
+    int rope_size,
+    float scale,
+    cudaStream_t stream = nullptr);
+
+// Backward of the above from the saved FP32 logsumexp.  The four gradient
+// buffers (BF16, shapes of the matching inputs) are overwritten.
+void mla_compressed_attention_backward_cuda(
+    __nv_bfloat16* query_latent_gradient,
+    __nv_bfloat16* query_rope_gradient,
+    __nv_bfloat16* kv_latent_gradient,
+    __nv_bfloat16* key_rope_gradient,
+    const __nv_bfloat16* output_gradient,
+    const __nv_bfloat16* output,
+    const float* logsumexp,
+    const __nv_bfloat16* query_latent,
+    const __nv_bfloat16* query_rope,
+    const __nv_bfloat16* kv_latent,
+    const __nv_bfloat16* key_rope,
+    int batch_size,
+    int sequence_length,
+    int heads,
+    int kv_rank,
+    int rope_size,
+    float scale,
+    cudaStream_t stream = nullptr);
+
+// FP32 elements the caller must provide as decode workspace:
+// B * H * splits * (C + 2).
+std::size_t mla_decode_workspace_elements(
+    int batch_size,
+    int heads,
+    int splits,
+    int kv_rank);
+
+// One packed BF16 query token [B,1,H,C+R] per sequence against a paged cache
+// [blocks,page,1,C+R]; block_table [B,pages_per_sequence] holds physical page
+// ids, cache_lengths [B] the number of valid tokens (>= 1).  output [B,1,H,C],
+// logsumexp [B*H].  page_size must be a multiple of 64.  `splits` bounds how
+// many partial results per (sequence, head) the workspace can hold.
+void mla_decode_forward_cuda(
+    __nv_bfloat16* output,
+    float* logsumexp,
+    const __nv_bfloat16* query,
+    const __nv_bfloat16* paged_kv_cache,
+    const int* block_table,
+    const int* cache_lengths,
+    float* workspace,
+    int batch_size,
+    int heads,
+    int kv_rank,
+    int rope_size,
+    int page_size,
+    int pages_per_sequence,
+    int splits,
+    float scale,
+    cudaStream_t stream = nullptr);
+
+// ---------------------------------------------------------------------------
+// Non-absorbed causal prefill / training path (no counterpart in the reference).
+//
+// Dense layout (cu_seqlens == nullptr): q_nope [B,S,H,128], q_pe [B,S,H,64],
+// k_nope [B,S,H,128], k_pe [B,S,1,64], v [B,S,H,128]; output [B,S,H,128],
+// logsumexp [B,H,S].  Pass batch_size = B, max_sequence_length = S,
+// total_tokens = B*S.
+//
+// Packed layout (cu_seqlens = device int32 [batch_size+1], cu_seqlens[0] = 0):
+// the leading [B,S] of every tensor becomes [total_tokens]; attention is causal
+// inside each sequence; logsumexp is [H,total_tokens].  Pass batch_size = number
+// of sequences and max_sequence_length >= the longest sequence.
+//
+// q_pe and k_pe are taken as given (already rotated).  nope_size, rope_size and
+// value_size must be 128, 64 and 128; scale must be positive.
+// ---------------------------------------------------------------------------
+void mla_prefill_forward_cuda(
+    __nv_bfloat16* output,
+    float* logsumexp,
+    const __nv_bfloat16* q_nope,
+    const __nv_bfloat16* q_pe,
+    const __nv_bfloat16* k_nope,
+    const __nv_bfloat16* k_pe,
+    const __nv_bfloat16* v,
+    const int* cu_seqlens,
+    int batch_size,
+    int max_sequence_length,
+    int total_tokens,
+    int heads,
+    int nope_size,
+    int rope_size,
+    int value_size,
+    float scale,
+    cudaStream_t stream = nullptr);
+
+// Bytes of caller-owned device scratch the backward needs.
+std::size_t mla_prefill_backward_workspace_bytes(
+    int batch_size,
+    int max_sequence_length,
+    int total_tokens,
+    int heads);
+
+// Backward of mla_prefill_forward_cuda.  Overwrites dq [..,H,192] (nope then
+// pe), dk_nope [..,H,128], dk_pe [..,1,64] (summed over the heads of this call)
+// and dv [..,H,128], all BF16.  The first total_tokens*64 FP32 values of the
+// workspace hold the unrounded dk_pe sums afterwards, for callers that shard
+// heads over several GPUs and add the partial sums themselves.
+void mla_prefill_backward_cuda(
+    __nv_bfloat16* dq,
+    __nv_bfloat16* dk_nope,
+    __nv_bfloat16* dk_pe,
+    __nv_bfloat16* dv,
+    const __nv_bfloat16* output_gradient,
+    const __nv_bfloat16* output,
+    const float* logsumexp,
+    const __nv_bfloat16* q_nope,
+    const __nv_bfloat16* q_pe,
+    const __nv_bfloat16* k_nope,
+    const __nv_bfloat16* k_pe,
+    const __nv_bfloat16* v,
+    const int* cu_seqlens,
+    void* workspace,
+    int batch_size,
+    int max_sequence_length,
+    int total_tokens,
+    int heads,
+    int nope_size,
+    int rope_size,
+    int value_size,
+    float scale,
+    cudaStream_t stream = nullptr);
+
+// Sticky device status shared by the kernels above: 0 = fine, 1 = a bounded
+// pipeline wait inside a kernel ran out (results of that launch are invalid).
+// Reading it synchronises the device; it is for tests and diagnosis, not for
+// the hot path.  `reset` clears it after reading.
+int mla_device_status(bool reset);
+
+}  // namespace dscuda
