@@ -1,0 +1,363 @@
+"""Throughput of the MLA path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload train|prefill]
+
+One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one
+batch of seeded synthetic input:
+
+* `train`   - causal MLA forward + backward, B=2, S=8192, H=128 per GPU, bf16
+              (q/k/v ~ N(0,1), dO ~ N(0,0.1));
+* `prefill` - causal MLA forward only, B=4, S=4096, H=128 per GPU.
+
+`value` is TFLOP/s counted on the algorithmic work (640 FLOP per causal
+(query,key) pair and head forward, 1664 backward), whole job, inputs resident in
+HBM.  `e2e` is the same metric through the host-buffer API: pinned host inputs
+copied to the device and the result read back inside the timed region.  The
+`decode` object reports the absorbed paged decode (batch 64, lengths uniform in
+[1024, 32768], 64-token pages, permuted page table) in GB/s of algorithmic
+bytes.  With several GPUs every rank runs the same per-GPU shard (heads are
+independent), there is no collective on the data path, and the job value is the
+sum over ranks divided by the slowest rank's time.
+
+`--impl reference` times the CPU oracle port of the reference's
+reference/python/mla.py on the host cores, on a bounded sample of the workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SCALE = 192 ** -0.5
+FWD_FLOP_PER_PAIR = 2 * (192 + 128)
+BWD_FLOP_PER_PAIR = 2 * (192 + 128 + 128 + 192 + 192)
+WORKLOADS = {
+    "train": dict(batch=2, seq=8192, heads=128, seed=2, dout_std=0.1, backward=True),
+    "prefill": dict(batch=4, seq=4096, heads=128, seed=1, dout_std=1.0, backward=False),
+}
+
+
+def causal_pairs(seq):
+    return seq * (seq + 1) // 2
+
+
+def workload_flops(w):
+    pairs = causal_pairs(w["seq"]) * w["batch"] * w["heads"]
+    return pairs * (FWD_FLOP_PER_PAIR + (BWD_FLOP_PER_PAIR if w["backward"] else 0))
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return dict(tensor=float(data["bf16_tflops_sustained"]), tensor_burst=float(data["bf16_tflops"]),
+                    hbm=float(data["hbm_gbs"]), source="measured")
+    return dict(tensor=1400.0, tensor_burst=1590.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+
+    def __init__(self, index):
+        self.index = index
+        self.clocks, self.masks, self.max_clock = [], 0, None
+        self.stop = threading.Event()
+        self.thread = threading.Thread(target=self.run, daemon=True)
+
+    def run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            physical = int(visible.split(",")[self.index]) if visible and visible.split(",")[self.index].isdigit() else self.index
+            handle = pynvml.nvmlDeviceGetHandleByIndex(physical)
+            self.max_clock = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            while not self.stop.is_set():
+                self.clocks.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                self.masks |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                self.stop.wait(0.01)
+        except Exception as error:           # reported, never fatal: the clocks are evidence, not the measurement
+            self.error = repr(error)
+
+    def __enter__(self):
+        self.thread.start()
+        time.sleep(0.05)
+        return self
+
+    def __exit__(self, *exc):
+        self.stop.set()
+        self.thread.join(timeout=10)
+
+    def summary(self):
+        if not self.clocks:
+            return dict(sm_mhz=None, sm_max_mhz=self.max_clock, reasons=[], samples=0, error=getattr(self, "error", None))
+        reasons = [name for name, bit in self.REASONS.items() if self.masks & bit]
+        return dict(sm_mhz=statistics.median(self.clocks), sm_min_mhz=min(self.clocks), sm_max_mhz=self.max_clock,
+                    reasons=reasons, samples=len(self.clocks))
+
+
+def device_inputs(w, device):
+    """Seeded N(0,1) bf16 inputs generated on the device (RoPE is input preparation
+    outside the kernels, which take already-rotated q_pe / k_pe)."""
+    g = torch.Generator(device=device).manual_seed(w["seed"])
+    b, s, h = w["batch"], w["seq"], w["heads"]
+
+    def draw(*shape, std=1.0):
+        return (torch.randn(*shape, device=device, generator=g, dtype=torch.float32) * std).bfloat16()
+
+    tensors = dict(q_nope=draw(b, s, h, 128), q_pe=draw(b, s, h, 64), k_nope=draw(b, s, h, 128), k_pe=draw(b, s, 1, 64),
+                   v=draw(b, s, h, 128))
+    if w["backward"]:
+        tensors["dout"] = draw(b, s, h, 128, std=w["dout_std"])
+    return tensors
+
+
+def time_steps(step, steps, warmup, barrier):
+    for _ in range(warmup):
+        step()
+    barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        step()
+    stop.record()
+    stop.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / 1e3
+
+
+def run_ours(args, rank, world, device):
+    from dscuda_b200 import mla
+    from oracle import mla_oracle as oracle  # cpu_baseline leg only
+
+    w = WORKLOADS[args.workload]
+    peaks = measured_peaks()
+    x = device_inputs(w, device)
+    fwd_in = (x["q_nope"], x["q_pe"], x["k_nope"], x["k_pe"], x["v"])
+    out = torch.empty_like(x["v"])
+    lse = torch.empty(w["batch"], w["heads"], w["seq"], device=device)
+    launches = 1
+    if w["backward"]:
+        workspace = mla.prefill_backward_workspace(w["batch"], w["seq"], w["batch"] * w["seq"], w["heads"], device)
+        grads = (torch.empty(w["batch"], w["seq"], w["heads"], 192, device=device, dtype=torch.bfloat16),
+                 torch.empty_like(x["k_nope"]), torch.empty_like(x["k_pe"]), torch.empty_like(x["v"]))
+        launches += mla.PREFILL_BACKWARD_LAUNCHES
+
+    def forward():
+        mla.prefill_forward(*fwd_in, SCALE, output=out, lse=lse)
+
+    def backward():
+        mla.prefill_backward(x["dout"], out, lse, *fwd_in, SCALE, workspace=workspace, grads=grads)
+
+    def step():
+        forward()
+        if w["backward"]:
+            backward()
+
+    if world > 1:
+        import torch.distributed as dist
+        barrier = dist.barrier
+    else:
+        def barrier():
+            return None
+
+    with ClockSampler(device.index) as sampler:
+        seconds = time_steps(step, args.steps, args.warmup, barrier)
+    clocks = sampler.summary()
+    assert mla.device_status() == 0, "a kernel reported a bounded-wait timeout"
+
+    # dominant call timed alone (same stream, CUDA events) for the roofline object
+    dominant = backward if w["backward"] else forward
+    dominant_seconds = time_steps(dominant, max(2, args.steps), 1, lambda: None) / max(2, args.steps)
+    dominant_flops = causal_pairs(w["seq"]) * w["batch"] * w["heads"] * (BWD_FLOP_PER_PAIR if w["backward"] else FWD_FLOP_PER_PAIR)
+
+    # end to end: pinned host inputs -> device -> kernels -> result back to the host
+    host = {k: torch.empty(v.shape, dtype=v.dtype, pin_memory=True).copy_(v) for k, v in x.items()}
+    staged = {k: torch.empty_like(v) for k, v in x.items()}
+    result_host = torch.empty(lse.shape, dtype=lse.dtype, pin_memory=True)
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    d2h = result_host.numel() * result_host.element_size()
+
+    def e2e_step():
+        for k in host:
+            staged[k].copy_(host[k], non_blocking=True)
+        ins = (staged["q_nope"], staged["q_pe"], staged["k_nope"], staged["k_pe"], staged["v"])
+        mla.prefill_forward(*ins, SCALE, output=out, lse=lse)
+        if w["backward"]:
+            mla.prefill_backward(staged["dout"], out, lse, *ins, SCALE, workspace=workspace, grads=grads)
+        result_host.copy_(lse, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_seconds = time_steps(e2e_step, e2e_steps, 1, barrier)
+
+    flops = workload_flops(w)
+    times = torch.tensor([seconds, e2e_seconds], device=device, dtype=torch.float64)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    seconds, e2e_seconds = float(times[0]), float(times[1])
+
+    decode = bench_decode(mla, oracle, device, peaks) if rank == 0 and not args.skip_decode else None
+    cpu = cpu_baseline(oracle, 12.0) if rank == 0 and not args.skip_cpu else None
+
+    if rank != 0:
+        return None
+    value = flops * world * args.steps / seconds / 1e12
+    achieved = dominant_flops / dominant_seconds / 1e12
+    line = {
+        "metric": "MLA fwd+bwd TFLOP/s (bf16 causal)" if w["backward"] else "MLA prefill fwd TFLOP/s (bf16 causal)",
+        "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: causal non-absorbed MLA, B={w['batch']} S={w['seq']} H={w['heads']} per GPU, "
+                               f"qk=128+64 (shared k_pe), v=128, seed {w['seed']}",
+                   "per_gpu_tflops": value / world, "sharding": "heads x batch per GPU, no collective on the data path",
+                   "l2": "inputs (>= 1.9 GB per step) exceed the 126 MB L2; no flush needed"},
+        "clocks": clocks,
+        "e2e": {"value": flops * world * e2e_steps / e2e_seconds / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "prefill backward (dQ + dK/dV kernels)" if w["backward"] else "attention_forward_kernel<3>",
+                     "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": achieved / peaks["tensor"],
+                     "peak_source": peaks["source"] + " sustained cuBLAS bf16", "frac_of_burst_peak": achieved / peaks["tensor_burst"],
+                     "traffic": None},
+        "cpu_baseline": cpu, "decode": decode,
+    }
+    return line
+
+
+def bench_decode(mla, oracle, device, peaks, steps=20, warmup=3, splits=16):
+    """Absorbed paged decode at batch 64, heads 128, lengths uniform in [1024, 32768] (seed 3)."""
+    query, cache, table, lengths = oracle.decode_inputs(seed=3, batch=64, heads=128)
+    total_tokens = int(lengths.sum())
+    q, c, t, n = (z.to(device) for z in (query, cache, table, lengths))
+    workspace = mla.decode_workspace(64, 128, splits, 512, device)
+    out = torch.empty(64, 1, 128, 512, device=device, dtype=torch.bfloat16)
+    lse = torch.empty(64, 128, 1, device=device)
+
+    def step():
+        mla.mla_decode(q, c, t, n, SCALE, splits=splits, workspace=workspace, output=out, lse=lse)
+
+    seconds = time_steps(step, steps, warmup, lambda: None) / steps
+    algorithmic = total_tokens * 576 * 2 + 64 * 128 * (576 + 512) * 2 + 64 * 128 * 4 + table.numel() * 4 + 64 * 4
+    flops = 2 * (576 + 512) * 128 * total_tokens
+    gbs = algorithmic / seconds / 1e9
+    return {"metric": "absorbed MLA decode HBM GB/s", "value": gbs, "unit": "GB/s", "us_per_step": seconds * 1e6,
+            "tokens": total_tokens, "algorithmic_bytes": algorithmic, "splits": splits, "tflops": flops / seconds / 1e12,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"],
+                         "peak_source": peaks["source"] + " copy bandwidth", "tensor_frac": flops / seconds / 1e12 / peaks["tensor_burst"]}}
+
+
+def cpu_baseline(oracle, budget_seconds):
+    """The oracle port on the host cores: B=1, S=256, H=16 fp32 forward+backward, repeated for about `budget_seconds`."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    q_nope, q_pe, k_nope, k_pe, v, dout = oracle.prefill_inputs(0, 1, 256, 16, dtype=torch.float32)
+    flops = causal_pairs(256) * 16 * (FWD_FLOP_PER_PAIR + BWD_FLOP_PER_PAIR)
+
+    def once():
+        out, lse = oracle.prefill_forward(q_nope, q_pe, k_nope, k_pe, v, SCALE)
+        oracle.prefill_backward(dout, out, lse, q_nope, q_pe, k_nope, k_pe, v, SCALE)
+
+    once()
+    runs, start = 0, time.perf_counter()
+    while time.perf_counter() - start < budget_seconds or runs < 3:
+        once()
+        runs += 1
+    seconds = (time.perf_counter() - start) / runs
+    return {"value": flops / seconds / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{runs} runs of B=1 S=256 H=16 fp32 forward+backward (oracle port of reference/python/mla.py), {seconds * 1e3:.1f} ms each"}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return None
+    from oracle import mla_oracle as oracle
+    w = WORKLOADS[args.workload]
+    torch.set_num_threads(os.cpu_count() or 1)
+    # bounded sample of the workload: the first 512 tokens of one sequence, 8 heads
+    seq, heads = 512, 8
+    q_nope, q_pe, k_nope, k_pe, v, dout = oracle.prefill_inputs(w["seed"], 1, seq, heads, dtype=torch.bfloat16, dout_std=w["dout_std"])
+    flops = causal_pairs(seq) * heads * (FWD_FLOP_PER_PAIR + (BWD_FLOP_PER_PAIR if w["backward"] else 0))
+
+    def step():
+        out, lse = oracle.prefill_forward(q_nope, q_pe, k_nope, k_pe, v, SCALE)
+        if w["backward"]:
+            oracle.prefill_backward(dout, out.bfloat16(), lse, q_nope, q_pe, k_nope, k_pe, v, SCALE)
+
+    for _ in range(args.warmup):
+        step()
+    start = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    seconds = time.perf_counter() - start
+    value = flops * args.steps / seconds / 1e12
+    sample = f"B=1 S={seq} H={heads} slice of the {args.workload} workload per step"
+    return {
+        "impl": "reference", "metric": "MLA fwd+bwd TFLOP/s (bf16 causal)" if w["backward"] else "MLA prefill fwd TFLOP/s (bf16 causal)",
+        "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: causal non-absorbed MLA, B={w['batch']} S={w['seq']} H={w['heads']} per GPU, "
+                               f"qk=128+64 (shared k_pe), v=128, seed {w['seed']}", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=10)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    parser.add_argument("--workload", default="train", choices=tuple(WORKLOADS))
+    parser.add_argument("--skip-decode", action="store_true")
+    parser.add_argument("--skip-cpu", action="store_true")
+    args = parser.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        line = run_reference(args, rank, world)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    try:
+        line = run_ours(args, rank, world, device)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,23 +1,820 @@
-// Placeholder translation unit, replaced by the real backward kernels.
+// Backward of the non-absorbed causal MLA attention for sm_100a.
+//
+// One call launches, on the caller's stream:
+//   1. a memset of the fp32 dk_pe accumulator (first total*64 floats of the workspace);
+//   2. delta_kernel:        delta[q] = sum_d dO[q,d] * O[q,d]            (fp32, LSE layout);
+//   3. backward_dq_kernel:  per 128-row query tile, over 64-key tiles
+//                           S = Q K^T, dP = dO V^T (tcgen05, fp32 in tensor memory),
+//                           P = exp(S*scale - LSE), dS = P (dP - delta) scale (registers),
+//                           dQ += dS K with dS fed from tensor memory;
+//   4. backward_dkdv_kernel: per 128-key tile, over 64-query tiles
+//                           S^T = K Q^T, dP^T = V dO^T, P^T, dS^T as above (one thread per key),
+//                           dV += P^T dO, dK += dS^T Q; the rotary 64 columns of dK are
+//                           added over heads with fp32 atomics into the accumulator;
+//   5. a conversion of that accumulator to bf16 dk_pe.
+//
+// S and dP are recomputed in both main kernels: a 128x192 dQ tile, a 128x192 dK
+// tile and a 128x128 dV tile plus the score tiles do not fit the 512 tensor
+// memory columns of one SM together, and splitting keeps every gradient a plain
+// single-writer store (only dk_pe, which sums over heads, uses atomics).
+//
+// Both main kernels: warps 0-3 and 4-7 are two softmax groups that take
+// alternate tiles, warp 8 issues the MMAs from one thread, warp 9 loads with
+// TMA.  Every wait is bounded.
 #include "mla.h"
+#include "cuda_common.h"
 #include "attention_internal.h"
+#include "sm100_primitives.cuh"
+#include "../common/tensor_map.h"
 
 #include <stdexcept>
 
 namespace dscuda {
-namespace internal {
-int backward_device_status(bool) { return 0; }
-}  // namespace internal
+namespace {
 
-std::size_t mla_prefill_backward_workspace_bytes(int, int, int total_tokens, int) {
-    return static_cast<std::size_t>(total_tokens) * 64 * sizeof(float);
+using namespace sm100;
+
+constexpr int BIG = 128;                     // rows of the stationary tile (TMEM lanes)
+constexpr int SUB = 64;                      // rows of the streamed tile
+constexpr int BIG_CHUNK = BIG * 128;         // 16 KB: [128 rows x 64 bf16]
+constexpr int SUB_CHUNK = SUB * 128;         //  8 KB: [64 rows x 64 bf16]
+constexpr int STAGES = 3;
+constexpr int STAGE_BYTES = 5 * SUB_CHUNK;   // 3 chunks of QK width + 2 chunks of V width
+constexpr int RESIDENT_BYTES = 5 * BIG_CHUNK;
+constexpr int MISC_BYTES = 2048;
+constexpr int SMEM_BYTES = RESIDENT_BYTES + STAGES * STAGE_BYTES + MISC_BYTES + 1024;
+constexpr int THREADS = 320;
+constexpr int MMA_WARP = 8;
+constexpr int LOAD_WARP = 9;
+constexpr int TMEM_COLUMNS = 512;
+constexpr float LOG2E = 1.4426950408889634F;
+
+__device__ int backward_status = 0;
+
+struct BackwardParams {
+    // 128-row boxes (stationary tiles) and 64-row boxes (streamed tiles) of the same tensors
+    CUtensorMap q_main_big, q_pe_big, k_main_big, k_pe_big, v_big, do_big;
+    CUtensorMap q_main_sub, q_pe_sub, k_main_sub, k_pe_sub, v_sub, do_sub;
+    __nv_bfloat16* dq;        // [rows, H, 192]
+    __nv_bfloat16* dk_nope;   // [rows, H, 128]
+    __nv_bfloat16* dv;        // [rows, H, 128]
+    float* dk_pe_acc;         // [rows, 64] fp32, zeroed before the launch
+    const float* lse;         // dense [B,H,S]; packed [H,total]
+    const float* delta;       // same layout as lse
+    const int* cu_seqlens;
+    int batch;
+    int max_seq;
+    int total;
+    int heads;
+    float scale;
+    float scale_log2;
+};
+
+struct BackwardBarriers {
+    uint64_t resident_full;
+    uint64_t stage_full[STAGES];
+    uint64_t stage_empty[STAGES];
+    uint64_t mma_a[2];          // tensor core -> softmax group: first score tile ready
+    uint64_t mma_b[2];          // tensor core -> softmax group: second score tile ready
+    uint64_t soft_a[2];         // softmax group -> tensor core: first bf16 operand stored
+    uint64_t soft_b[2];         // softmax group -> tensor core: second bf16 operand stored
+    uint64_t final_full;
+    uint32_t tmem_base;
+    int abort_flag;
+    float2 lse_delta[STAGES][SUB];   // dK/dV kernel: (LSE * log2 e, delta) of the streamed queries
+};
+static_assert(sizeof(BackwardBarriers) <= MISC_BYTES, "barrier block too large");
+
+// Maps a linear block index to (sequence, block inside the sequence).  Dense:
+// blockIdx.z is the batch entry.  Packed: walk cu_seqlens.  Returns false when
+// the index is past the last block.
+__device__ __forceinline__ bool locate_block(const BackwardParams& p, int rows_per_block, int index, int& row0, int& length,
+                                             int& block, int& blocks_in_sequence, size_t& lse_offset, int head) {
+    if (p.cu_seqlens == nullptr) {
+        const int b = blockIdx.z;
+        row0 = b * p.max_seq;
+        length = p.max_seq;
+        blocks_in_sequence = (length + rows_per_block - 1) / rows_per_block;
+        block = index;
+        lse_offset = (static_cast<size_t>(b) * p.heads + head) * p.max_seq;
+        return block < blocks_in_sequence;
+    }
+    for (int sequence = 0; sequence < p.batch; ++sequence) {
+        const int begin = p.cu_seqlens[sequence];
+        const int tokens = p.cu_seqlens[sequence + 1] - begin;
+        const int blocks = (tokens + rows_per_block - 1) / rows_per_block;
+        if (index < blocks) {
+            row0 = begin;
+            length = tokens;
+            block = index;
+            blocks_in_sequence = blocks;
+            lse_offset = static_cast<size_t>(head) * p.total + begin;
+            return true;
+        }
+        index -= blocks;
+    }
+    return false;
 }
 
-void mla_prefill_backward_cuda(__nv_bfloat16*, __nv_bfloat16*, __nv_bfloat16*, __nv_bfloat16*, const __nv_bfloat16*,
-                               const __nv_bfloat16*, const float*, const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*,
-                               const __nv_bfloat16*, const __nv_bfloat16*, const int*, void*, int, int, int, int, int, int, int, float,
-                               cudaStream_t) {
-    throw std::runtime_error("mla_prefill_backward_cuda: not built yet");
+__device__ __forceinline__ void init_barriers(BackwardBarriers* bars, uint32_t stage_full_arrivals) {
+    mbar_init(smem_u32(&bars->resident_full), 1);
+    for (int i = 0; i < STAGES; ++i) {
+        mbar_init(smem_u32(&bars->stage_full[i]), stage_full_arrivals);
+        mbar_init(smem_u32(&bars->stage_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+        mbar_init(smem_u32(&bars->mma_a[i]), 1);
+        mbar_init(smem_u32(&bars->mma_b[i]), 1);
+        mbar_init(smem_u32(&bars->soft_a[i]), BIG);
+        mbar_init(smem_u32(&bars->soft_b[i]), BIG);
+    }
+    mbar_init(smem_u32(&bars->final_full), 1);
+    bars->abort_flag = 0;
+    mbar_init_fence();
+}
+
+__device__ __forceinline__ void store_bf16_row(__nv_bfloat16* dst, const uint32_t* values, int count, float factor) {
+    for (int e = 0; e < count; e += 8) {
+        uint4 vec;
+        vec.x = pack_bf16x2(__uint_as_float(values[e]) * factor, __uint_as_float(values[e + 1]) * factor);
+        vec.y = pack_bf16x2(__uint_as_float(values[e + 2]) * factor, __uint_as_float(values[e + 3]) * factor);
+        vec.z = pack_bf16x2(__uint_as_float(values[e + 4]) * factor, __uint_as_float(values[e + 5]) * factor);
+        vec.w = pack_bf16x2(__uint_as_float(values[e + 6]) * factor, __uint_as_float(values[e + 7]) * factor);
+        *reinterpret_cast<uint4*>(dst + e) = vec;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// delta[q] = sum_d dO[q,d] * O[q,d]; one warp per (row, head).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) delta_kernel(float* delta, const __nv_bfloat16* dout, const __nv_bfloat16* out, const int* cu_seqlens,
+                                                    int batch, int max_seq, int total, int heads) {
+    const size_t pairs = static_cast<size_t>(total) * heads;
+    const size_t warp_stride = static_cast<size_t>(gridDim.x) * (blockDim.x / 32);
+    const int lane = threadIdx.x % 32;
+    for (size_t pair = static_cast<size_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32; pair < pairs; pair += warp_stride) {
+        const uint2 a = *reinterpret_cast<const uint2*>(dout + pair * 128 + lane * 4);
+        const uint2 b = *reinterpret_cast<const uint2*>(out + pair * 128 + lane * 4);
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+        const float2 a0 = __bfloat1622float2(a2[0]), a1 = __bfloat1622float2(a2[1]);
+        const float2 b0 = __bfloat1622float2(b2[0]), b1 = __bfloat1622float2(b2[1]);
+        float sum = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            sum += __shfl_xor_sync(0xffffffffU, sum, offset);
+        }
+        if (lane == 0) {
+            const size_t row = pair / heads;
+            const int head = static_cast<int>(pair % heads);
+            size_t index;
+            if (cu_seqlens == nullptr) {
+                const size_t b_index = row / max_seq;
+                index = (b_index * heads + head) * max_seq + row % max_seq;
+            } else {
+                index = static_cast<size_t>(head) * total + row;
+            }
+            delta[index] = sum;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// dk_pe accumulator -> bf16
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) convert_dk_pe_kernel(__nv_bfloat16* dk_pe, const float* acc, size_t elements) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; index < elements; index += stride) {
+        dk_pe[index] = __float2bfloat16(acc[index]);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// dQ kernel: stationary 128 query rows (Q 3 chunks, dO 2 chunks), streamed
+// 64-key tiles (K 3 chunks, V 2 chunks).
+// Tensor memory: set g in {0,1}: S at 128g, dP at 128g+64; dQ at 256..447.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS, 1) backward_dq_kernel(const __grid_constant__ BackwardParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    if (*reinterpret_cast<volatile int*>(&backward_status) != 0) {
+        return;
+    }
+    const int head = blockIdx.y;
+    int row0, length, block, blocks_in_sequence;
+    size_t lse_offset;
+    if (!locate_block(p, BIG, blockIdx.x, row0, length, block, blocks_in_sequence, lse_offset, head)) {
+        return;
+    }
+    block = blocks_in_sequence - 1 - block;            // longest first
+    const int q_start = block * BIG;
+    const int kv_end = min(length, q_start + BIG);
+    const int tile_count = (kv_end + SUB - 1) / SUB;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023U) & ~1023U;
+    uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t q_smem = smem_base;                          // 3 chunks
+    const uint32_t do_smem = smem_base + 3 * BIG_CHUNK;         // 2 chunks
+    const uint32_t stage_smem = smem_base + RESIDENT_BYTES;
+    BackwardBarriers* bars = reinterpret_cast<BackwardBarriers*>(smem_aligned + RESIDENT_BYTES + STAGES * STAGE_BYTES);
+    volatile int* abort_flag = &bars->abort_flag;
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+
+    if (threadIdx.x == 0) {
+        init_barriers(bars, 1);
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc(smem_u32(&bars->tmem_base), TMEM_COLUMNS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+    constexpr uint32_t TMEM_DQ = 256;
+
+    if (warp == LOAD_WARP) {
+        if (lane == 0) {
+            const uint32_t bar = smem_u32(&bars->resident_full);
+            mbar_arrive_expect_tx(bar, RESIDENT_BYTES);
+            const int y = row0 + q_start;
+            tma_load_2d(q_smem, &p.q_main_big, bar, head * 128, y);
+            tma_load_2d(q_smem + BIG_CHUNK, &p.q_main_big, bar, head * 128 + 64, y);
+            tma_load_2d(q_smem + 2 * BIG_CHUNK, &p.q_pe_big, bar, head * 64, y);
+            tma_load_2d(do_smem, &p.do_big, bar, head * 128, y);
+            tma_load_2d(do_smem + BIG_CHUNK, &p.do_big, bar, head * 128 + 64, y);
+            for (int j = 0; j < tile_count; ++j) {
+                const int stage = j % STAGES;
+                const int use = j / STAGES;
+                if (use > 0 && !mbar_wait(smem_u32(&bars->stage_empty[stage]), (use - 1) & 1, abort_flag, &backward_status)) {
+                    break;
+                }
+                const uint32_t full = smem_u32(&bars->stage_full[stage]);
+                mbar_arrive_expect_tx(full, STAGE_BYTES);
+                const uint32_t dst = stage_smem + stage * STAGE_BYTES;
+                const int ky = row0 + j * SUB;
+                tma_load_2d(dst, &p.k_main_sub, full, head * 128, ky);
+                tma_load_2d(dst + SUB_CHUNK, &p.k_main_sub, full, head * 128 + 64, ky);
+                tma_load_2d(dst + 2 * SUB_CHUNK, &p.k_pe_sub, full, 0, ky);
+                tma_load_2d(dst + 3 * SUB_CHUNK, &p.v_sub, full, head * 128, ky);
+                tma_load_2d(dst + 4 * SUB_CHUNK, &p.v_sub, full, head * 128 + 64, ky);
+            }
+        }
+    } else if (warp == MMA_WARP) {
+        if (lane == 0) {
+            constexpr uint32_t IDESC_SCORE = make_idesc_bf16(BIG, SUB, false, false);
+            constexpr uint32_t IDESC_DQ = make_idesc_bf16(BIG, 192, false, true);
+            bool alive = mbar_wait(smem_u32(&bars->resident_full), 0, abort_flag, &backward_status);
+            auto issue_scores = [&](int j) {
+                const int stage = j % STAGES;
+                alive = mbar_wait(smem_u32(&bars->stage_full[stage]), (j / STAGES) & 1, abort_flag, &backward_status);
+                if (!alive) {
+                    return;
+                }
+                tc_fence_after_sync();
+                const uint32_t k_smem = stage_smem + stage * STAGE_BYTES;
+                const uint32_t v_smem = k_smem + 3 * SUB_CHUNK;
+                const uint32_t s_tmem = tmem_base + (j & 1) * 128;
+#pragma unroll
+                for (int c = 0; c < 3; ++c) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        mma_ss(s_tmem, make_kmajor_desc(q_smem + c * BIG_CHUNK + k * 32), make_kmajor_desc(k_smem + c * SUB_CHUNK + k * 32),
+                               IDESC_SCORE, (c | k) != 0 ? 1U : 0U);
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        mma_ss(s_tmem + 64, make_kmajor_desc(do_smem + c * BIG_CHUNK + k * 32),
+                               make_kmajor_desc(v_smem + c * SUB_CHUNK + k * 32), IDESC_SCORE, (c | k) != 0 ? 1U : 0U);
+                    }
+                }
+                mma_commit(smem_u32(&bars->mma_a[j & 1]));
+            };
+            if (alive) {
+                issue_scores(0);
+            }
+            for (int j = 0; j < tile_count && alive; ++j) {
+                if (j + 1 < tile_count) {
+                    issue_scores(j + 1);
+                    if (!alive) {
+                        break;
+                    }
+                }
+                alive = mbar_wait(smem_u32(&bars->soft_a[j & 1]), (j >> 1) & 1, abort_flag, &backward_status);
+                if (!alive) {
+                    break;
+                }
+                tc_fence_after_sync();
+                const int stage = j % STAGES;
+                const uint32_t k_smem = stage_smem + stage * STAGE_BYTES;
+                const uint32_t ds_tmem = tmem_base + (j & 1) * 128 + 64;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    mma_ts(tmem_base + TMEM_DQ, ds_tmem + k * 8, make_smem_desc(k_smem + k * 2048, SUB_CHUNK, 1024), IDESC_DQ,
+                           (j | k) != 0 ? 1U : 0U);
+                }
+                mma_commit(smem_u32(&bars->stage_empty[stage]));
+            }
+            if (alive) {
+                mma_commit(smem_u32(&bars->final_full));
+            }
+        }
+    } else {
+        const int group = warp / 4;
+        const int r = threadIdx.x % BIG;
+        const uint32_t lane_base = static_cast<uint32_t>((warp % 4) * 32) << 16;
+        const int q_pos = q_start + r;
+        const int q_safe = min(q_pos, length - 1);
+        const float lse2 = p.lse[lse_offset + q_safe] * LOG2E;
+        const float delta = p.delta[lse_offset + q_safe];
+        bool alive = true;
+        for (int j = group; j < tile_count; j += 2) {
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->mma_a[group]), (j >> 1) & 1, abort_flag, &backward_status));
+            if (!alive) {
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t s_tmem = tmem_base + lane_base + group * 128;
+            uint32_t sb[SUB], dp[SUB];
+            tmem_ld_x32(s_tmem, sb);
+            tmem_ld_x32(s_tmem + 32, sb + 32);
+            tmem_ld_x32(s_tmem + 64, dp);
+            tmem_ld_x32(s_tmem + 96, dp + 32);
+            tmem_wait_ld();
+            const int key0 = j * SUB;
+            const bool masked = key0 + SUB - 1 > q_start;
+            uint32_t packed[SUB / 2];
+#pragma unroll
+            for (int n = 0; n < SUB; n += 2) {
+                float p0 = exp2_approx(fmaf(__uint_as_float(sb[n]), p.scale_log2, -lse2));
+                float p1 = exp2_approx(fmaf(__uint_as_float(sb[n + 1]), p.scale_log2, -lse2));
+                if (masked) {
+                    p0 = key0 + n <= q_pos ? p0 : 0.0F;
+                    p1 = key0 + n + 1 <= q_pos ? p1 : 0.0F;
+                }
+                const float d0 = p0 * (__uint_as_float(dp[n]) - delta) * p.scale;
+                const float d1 = p1 * (__uint_as_float(dp[n + 1]) - delta) * p.scale;
+                packed[n / 2] = pack_bf16x2(d0, d1);
+            }
+            tmem_st_x32(s_tmem + 64, packed);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bars->soft_a[group]));
+        }
+        if (alive) {
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->final_full), 0, abort_flag, &backward_status));
+        }
+        if (alive) {
+            tc_fence_after_sync();
+            const bool valid = q_pos < length;
+            __nv_bfloat16* dq_row = p.dq + (static_cast<size_t>(row0 + q_pos) * p.heads + head) * 192 + group * 96;
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                uint32_t values[32];
+                tmem_ld_x32(tmem_base + lane_base + TMEM_DQ + group * 96 + c * 32, values);
+                tmem_wait_ld();
+                if (valid) {
+                    store_bf16_row(dq_row + c * 32, values, 32, 1.0F);
+                }
+            }
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag != 0) {
+        for (int k = 0; k < 64; ++k) {
+            __nanosleep(1000);
+        }
+    }
+    if (warp == MMA_WARP) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLUMNS);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// dK/dV kernel: stationary 128 keys (K 3 chunks, V 2 chunks), streamed 64-query
+// tiles (Q 3 chunks, dO 2 chunks, LSE and delta of those queries).
+// Tensor memory: dV at 0..127, dK at 128..319, three 64-column score buffers
+// X0..X2 at 320/384/448.  Tile t (relative) puts S^T in X[(2t)%3] and dP^T in
+// X[(2t+1)%3]; P^T and dS^T overwrite them in place as bf16.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_constant__ BackwardParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    if (*reinterpret_cast<volatile int*>(&backward_status) != 0) {
+        return;
+    }
+    const int head = blockIdx.y;
+    int row0, length, block, blocks_in_sequence;
+    size_t lse_offset;
+    if (!locate_block(p, BIG, blockIdx.x, row0, length, block, blocks_in_sequence, lse_offset, head)) {
+        return;
+    }
+    const int key_start = block * BIG;                 // block 0 has the most queries: longest first
+    const int first_tile = key_start / SUB;
+    const int tile_count = (length + SUB - 1) / SUB - first_tile;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023U) & ~1023U;
+    uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t k_smem = smem_base;                          // 3 chunks
+    const uint32_t v_smem = smem_base + 3 * BIG_CHUNK;          // 2 chunks
+    const uint32_t stage_smem = smem_base + RESIDENT_BYTES;
+    BackwardBarriers* bars = reinterpret_cast<BackwardBarriers*>(smem_aligned + RESIDENT_BYTES + STAGES * STAGE_BYTES);
+    volatile int* abort_flag = &bars->abort_flag;
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+
+    if (threadIdx.x == 0) {
+        // stage_full needs two arrivals here: the TMA transaction and the LSE/delta rows
+        init_barriers(bars, 2);
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc(smem_u32(&bars->tmem_base), TMEM_COLUMNS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+    constexpr uint32_t TMEM_DV = 0;
+    constexpr uint32_t TMEM_DK = 128;
+    constexpr uint32_t TMEM_X = 320;
+
+    if (warp == LOAD_WARP) {
+        if (lane == 0) {
+            const uint32_t bar = smem_u32(&bars->resident_full);
+            mbar_arrive_expect_tx(bar, RESIDENT_BYTES);
+            const int y = row0 + key_start;
+            tma_load_2d(k_smem, &p.k_main_big, bar, head * 128, y);
+            tma_load_2d(k_smem + BIG_CHUNK, &p.k_main_big, bar, head * 128 + 64, y);
+            tma_load_2d(k_smem + 2 * BIG_CHUNK, &p.k_pe_big, bar, 0, y);
+            tma_load_2d(v_smem, &p.v_big, bar, head * 128, y);
+            tma_load_2d(v_smem + BIG_CHUNK, &p.v_big, bar, head * 128 + 64, y);
+        }
+        bool alive = true;
+        for (int t = 0; t < tile_count && alive; ++t) {
+            const int stage = t % STAGES;
+            const int use = t / STAGES;
+            if (use > 0) {
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->stage_empty[stage]), (use - 1) & 1, abort_flag, &backward_status));
+                if (!alive) {
+                    break;
+                }
+            }
+            const int q0 = (first_tile + t) * SUB;
+            const uint32_t full = smem_u32(&bars->stage_full[stage]);
+            if (lane == 0) {
+                mbar_arrive_expect_tx(full, STAGE_BYTES);
+                const uint32_t dst = stage_smem + stage * STAGE_BYTES;
+                const int qy = row0 + q0;
+                tma_load_2d(dst, &p.q_main_sub, full, head * 128, qy);
+                tma_load_2d(dst + SUB_CHUNK, &p.q_main_sub, full, head * 128 + 64, qy);
+                tma_load_2d(dst + 2 * SUB_CHUNK, &p.q_pe_sub, full, head * 64, qy);
+                tma_load_2d(dst + 3 * SUB_CHUNK, &p.do_sub, full, head * 128, qy);
+                tma_load_2d(dst + 4 * SUB_CHUNK, &p.do_sub, full, head * 128 + 64, qy);
+            }
+#pragma unroll
+            for (int e = 0; e < SUB / 32; ++e) {
+                const int n = e * 32 + lane;
+                const int q_pos = q0 + n;
+                float2 value = make_float2(0.0F, 0.0F);
+                if (q_pos < length) {
+                    value.x = p.lse[lse_offset + q_pos] * LOG2E;
+                    value.y = p.delta[lse_offset + q_pos];
+                }
+                bars->lse_delta[stage][n] = value;
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(full);
+            }
+        }
+    } else if (warp == MMA_WARP) {
+        if (lane == 0) {
+            constexpr uint32_t IDESC_SCORE = make_idesc_bf16(BIG, SUB, false, false);
+            constexpr uint32_t IDESC_DV = make_idesc_bf16(BIG, 128, false, true);
+            constexpr uint32_t IDESC_DK = make_idesc_bf16(BIG, 192, false, true);
+            bool alive = mbar_wait(smem_u32(&bars->resident_full), 0, abort_flag, &backward_status);
+            auto x_buffer = [&](int index) -> uint32_t { return tmem_base + TMEM_X + (index % 3) * 64; };
+            // S^T(t) = K Q_t^T
+            auto issue_st = [&](int t) {
+                const int stage = t % STAGES;
+                alive = mbar_wait(smem_u32(&bars->stage_full[stage]), (t / STAGES) & 1, abort_flag, &backward_status);
+                if (!alive) {
+                    return;
+                }
+                tc_fence_after_sync();
+                const uint32_t q_smem = stage_smem + stage * STAGE_BYTES;
+#pragma unroll
+                for (int c = 0; c < 3; ++c) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        mma_ss(x_buffer(2 * t), make_kmajor_desc(k_smem + c * BIG_CHUNK + k * 32),
+                               make_kmajor_desc(q_smem + c * SUB_CHUNK + k * 32), IDESC_SCORE, (c | k) != 0 ? 1U : 0U);
+                    }
+                }
+                mma_commit(smem_u32(&bars->mma_a[t & 1]));
+            };
+            // dP^T(t) = V dO_t^T   (the stage is already known to be full)
+            auto issue_dpt = [&](int t) {
+                const uint32_t do_smem = stage_smem + (t % STAGES) * STAGE_BYTES + 3 * SUB_CHUNK;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        mma_ss(x_buffer(2 * t + 1), make_kmajor_desc(v_smem + c * BIG_CHUNK + k * 32),
+                               make_kmajor_desc(do_smem + c * SUB_CHUNK + k * 32), IDESC_SCORE, (c | k) != 0 ? 1U : 0U);
+                    }
+                }
+                mma_commit(smem_u32(&bars->mma_b[t & 1]));
+            };
+            if (alive) {
+                issue_st(0);
+            }
+            if (alive) {
+                issue_dpt(0);
+            }
+            for (int t = 0; t < tile_count && alive; ++t) {
+                const int stage = t % STAGES;
+                const uint32_t parity = (t >> 1) & 1;
+                if (t + 1 < tile_count) {
+                    issue_st(t + 1);
+                    if (!alive) {
+                        break;
+                    }
+                }
+                alive = mbar_wait(smem_u32(&bars->soft_a[t & 1]), parity, abort_flag, &backward_status);
+                if (!alive) {
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t q_smem = stage_smem + stage * STAGE_BYTES;
+                const uint32_t do_smem = q_smem + 3 * SUB_CHUNK;
+                // dV += P^T dO_t
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    mma_ts(tmem_base + TMEM_DV, x_buffer(2 * t) + k * 8, make_smem_desc(do_smem + k * 2048, SUB_CHUNK, 1024), IDESC_DV,
+                           (t | k) != 0 ? 1U : 0U);
+                }
+                if (t + 1 < tile_count) {
+                    issue_dpt(t + 1);
+                }
+                alive = mbar_wait(smem_u32(&bars->soft_b[t & 1]), parity, abort_flag, &backward_status);
+                if (!alive) {
+                    break;
+                }
+                tc_fence_after_sync();
+                // dK += dS^T Q_t
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    mma_ts(tmem_base + TMEM_DK, x_buffer(2 * t + 1) + k * 8, make_smem_desc(q_smem + k * 2048, SUB_CHUNK, 1024), IDESC_DK,
+                           (t | k) != 0 ? 1U : 0U);
+                }
+                mma_commit(smem_u32(&bars->stage_empty[stage]));
+            }
+            if (alive) {
+                mma_commit(smem_u32(&bars->final_full));
+            }
+        }
+    } else {
+        const int group = warp / 4;
+        const int r = threadIdx.x % BIG;
+        const uint32_t lane_base = static_cast<uint32_t>((warp % 4) * 32) << 16;
+        const int key_pos = key_start + r;
+        bool alive = true;
+        for (int t = group; t < tile_count; t += 2) {
+            const int stage = t % STAGES;
+            const uint32_t parity = (t >> 1) & 1;
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->stage_full[stage]), (t / STAGES) & 1, abort_flag, &backward_status) &&
+                                                mbar_wait(smem_u32(&bars->mma_a[group]), parity, abort_flag, &backward_status));
+            if (!alive) {
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t st_tmem = tmem_base + lane_base + TMEM_X + ((2 * t) % 3) * 64;
+            const uint32_t dpt_tmem = tmem_base + lane_base + TMEM_X + ((2 * t + 1) % 3) * 64;
+            const float2* ld = bars->lse_delta[stage];
+            const int q0 = (first_tile + t) * SUB;
+            const bool masked = q0 < key_start + BIG || q0 + SUB > length;
+            uint32_t sb[SUB];
+            float prob[SUB];
+            tmem_ld_x32(st_tmem, sb);
+            tmem_ld_x32(st_tmem + 32, sb + 32);
+            tmem_wait_ld();
+            uint32_t packed[SUB / 2];
+#pragma unroll
+            for (int n = 0; n < SUB; ++n) {
+                float value = exp2_approx(fmaf(__uint_as_float(sb[n]), p.scale_log2, -ld[n].x));
+                if (masked) {
+                    value = (key_pos <= q0 + n && q0 + n < length) ? value : 0.0F;
+                }
+                prob[n] = value;
+            }
+#pragma unroll
+            for (int n = 0; n < SUB; n += 2) {
+                packed[n / 2] = pack_bf16x2(prob[n], prob[n + 1]);
+            }
+            tmem_st_x32(st_tmem, packed);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bars->soft_a[group]));
+
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->mma_b[group]), parity, abort_flag, &backward_status));
+            if (!alive) {
+                break;
+            }
+            tc_fence_after_sync();
+            tmem_ld_x32(dpt_tmem, sb);
+            tmem_ld_x32(dpt_tmem + 32, sb + 32);
+            tmem_wait_ld();
+#pragma unroll
+            for (int n = 0; n < SUB; n += 2) {
+                const float d0 = prob[n] * (__uint_as_float(sb[n]) - ld[n].y) * p.scale;
+                const float d1 = prob[n + 1] * (__uint_as_float(sb[n + 1]) - ld[n + 1].y) * p.scale;
+                packed[n / 2] = pack_bf16x2(d0, d1);
+            }
+            tmem_st_x32(dpt_tmem, packed);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bars->soft_b[group]));
+        }
+        if (alive) {
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->final_full), 0, abort_flag, &backward_status));
+        }
+        if (alive) {
+            tc_fence_after_sync();
+            const bool valid = key_pos < length;
+            const size_t row = static_cast<size_t>(row0 + key_pos);
+            if (group == 0) {
+                __nv_bfloat16* dv_row = p.dv + (row * p.heads + head) * 128;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t values[32];
+                    tmem_ld_x32(tmem_base + lane_base + TMEM_DV + c * 32, values);
+                    tmem_wait_ld();
+                    if (valid) {
+                        store_bf16_row(dv_row + c * 32, values, 32, 1.0F);
+                    }
+                }
+            } else {
+                __nv_bfloat16* dk_row = p.dk_nope + (row * p.heads + head) * 128;
+#pragma unroll
+                for (int c = 0; c < 6; ++c) {
+                    uint32_t values[32];
+                    tmem_ld_x32(tmem_base + lane_base + TMEM_DK + c * 32, values);
+                    tmem_wait_ld();
+                    if (valid) {
+                        if (c < 4) {
+                            store_bf16_row(dk_row + c * 32, values, 32, 1.0F);
+                        } else {
+                            float* acc = p.dk_pe_acc + row * 64 + (c - 4) * 32;
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                atomicAdd(acc + e, __uint_as_float(values[e]));
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag != 0) {
+        for (int k = 0; k < 64; ++k) {
+            __nanosleep(1000);
+        }
+    }
+    if (warp == MMA_WARP) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLUMNS);
+    }
+}
+
+void configure_kernels() {
+    static bool done[16] = {};
+    int device = 0;
+    CUDA_CHECK(cudaGetDevice(&device));
+    if (device < 16 && done[device]) {
+        return;
+    }
+    CUDA_CHECK(cudaFuncSetAttribute(backward_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    CUDA_CHECK(cudaFuncSetAttribute(backward_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    if (device < 16) {
+        done[device] = true;
+    }
+}
+
+std::size_t accumulator_bytes(int total_tokens) {
+    // fp32 dk_pe sums, rounded up so that the delta array behind it stays 256-byte aligned
+    return (static_cast<std::size_t>(total_tokens) * 64 * sizeof(float) + 255) / 256 * 256;
+}
+
+}  // namespace
+
+namespace internal {
+
+int backward_device_status(bool reset) {
+    int status = 0;
+    CUDA_CHECK(cudaDeviceSynchronize());
+    CUDA_CHECK(cudaMemcpyFromSymbol(&status, backward_status, sizeof(int)));
+    if (reset && status != 0) {
+        const int zero = 0;
+        CUDA_CHECK(cudaMemcpyToSymbol(backward_status, &zero, sizeof(int)));
+    }
+    return status;
+}
+
+}  // namespace internal
+
+std::size_t mla_prefill_backward_workspace_bytes(int batch_size, int max_sequence_length, int total_tokens, int heads) {
+    (void)batch_size;
+    (void)max_sequence_length;
+    if (total_tokens <= 0 || heads <= 0) {
+        return 0;
+    }
+    return accumulator_bytes(total_tokens) + static_cast<std::size_t>(total_tokens) * heads * sizeof(float);
+}
+
+void mla_prefill_backward_cuda(__nv_bfloat16* dq, __nv_bfloat16* dk_nope, __nv_bfloat16* dk_pe, __nv_bfloat16* dv,
+                               const __nv_bfloat16* output_gradient, const __nv_bfloat16* output, const float* logsumexp,
+                               const __nv_bfloat16* q_nope, const __nv_bfloat16* q_pe, const __nv_bfloat16* k_nope, const __nv_bfloat16* k_pe,
+                               const __nv_bfloat16* v, const int* cu_seqlens, void* workspace, int batch_size, int max_sequence_length,
+                               int total_tokens, int heads, int nope_size, int rope_size, int value_size, float scale, cudaStream_t stream) {
+    internal::check_prefill_shape(cu_seqlens, batch_size, max_sequence_length, total_tokens, heads, nope_size, rope_size, value_size, scale);
+    for (const void* pointer : {static_cast<const void*>(dq), static_cast<const void*>(dk_nope), static_cast<const void*>(dk_pe),
+                                static_cast<const void*>(dv), static_cast<const void*>(output_gradient), static_cast<const void*>(output),
+                                static_cast<const void*>(logsumexp), static_cast<const void*>(q_nope), static_cast<const void*>(q_pe),
+                                static_cast<const void*>(k_nope), static_cast<const void*>(k_pe), static_cast<const void*>(v),
+                                static_cast<const void*>(workspace)}) {
+        if (pointer == nullptr) {
+            throw std::invalid_argument("null tensor pointer");
+        }
+        if ((reinterpret_cast<std::uintptr_t>(pointer) & 15U) != 0) {
+            throw std::invalid_argument("tensor pointers must be 16-byte aligned");
+        }
+    }
+    float* accumulator = static_cast<float*>(workspace);
+    float* delta = reinterpret_cast<float*>(static_cast<char*>(workspace) + accumulator_bytes(total_tokens));
+
+    BackwardParams params{};
+    const std::uint64_t rows = static_cast<std::uint64_t>(total_tokens);
+    const std::uint64_t wide = static_cast<std::uint64_t>(heads) * 128;
+    const std::uint64_t narrow = static_cast<std::uint64_t>(heads) * 64;
+    params.q_main_big = make_bf16_tile_map(q_nope, rows, wide, wide, BIG);
+    params.q_pe_big = make_bf16_tile_map(q_pe, rows, narrow, narrow, BIG);
+    params.k_main_big = make_bf16_tile_map(k_nope, rows, wide, wide, BIG);
+    params.k_pe_big = make_bf16_tile_map(k_pe, rows, 64, 64, BIG);
+    params.v_big = make_bf16_tile_map(v, rows, wide, wide, BIG);
+    params.do_big = make_bf16_tile_map(output_gradient, rows, wide, wide, BIG);
+    params.q_main_sub = make_bf16_tile_map(q_nope, rows, wide, wide, SUB);
+    params.q_pe_sub = make_bf16_tile_map(q_pe, rows, narrow, narrow, SUB);
+    params.k_main_sub = make_bf16_tile_map(k_nope, rows, wide, wide, SUB);
+    params.k_pe_sub = make_bf16_tile_map(k_pe, rows, 64, 64, SUB);
+    params.v_sub = make_bf16_tile_map(v, rows, wide, wide, SUB);
+    params.do_sub = make_bf16_tile_map(output_gradient, rows, wide, wide, SUB);
+    params.dq = dq;
+    params.dk_nope = dk_nope;
+    params.dv = dv;
+    params.dk_pe_acc = accumulator;
+    params.lse = logsumexp;
+    params.delta = delta;
+    params.cu_seqlens = cu_seqlens;
+    params.batch = batch_size;
+    params.max_seq = max_sequence_length;
+    params.total = total_tokens;
+    params.heads = heads;
+    params.scale = scale;
+    params.scale_log2 = scale * LOG2E;
+    configure_kernels();
+
+    CUDA_CHECK(cudaMemsetAsync(accumulator, 0, static_cast<std::size_t>(total_tokens) * 64 * sizeof(float), stream));
+    const std::size_t pairs = static_cast<std::size_t>(total_tokens) * heads;
+    const unsigned delta_blocks = static_cast<unsigned>(pairs / 8 + 1 < 148 * 32 ? pairs / 8 + 1 : 148 * 32);
+    delta_kernel<<<delta_blocks, 256, 0, stream>>>(delta, output_gradient, output, cu_seqlens, batch_size, max_sequence_length, total_tokens, heads);
+    CUDA_CHECK(cudaGetLastError());
+
+    dim3 grid;
+    if (cu_seqlens == nullptr) {
+        grid = dim3((max_sequence_length + BIG - 1) / BIG, heads, batch_size);
+    } else {
+        grid = dim3(total_tokens / BIG + batch_size, heads, 1);
+    }
+    backward_dq_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(params);
+    CUDA_CHECK(cudaGetLastError());
+    backward_dkdv_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(params);
+    CUDA_CHECK(cudaGetLastError());
+    const std::size_t elements = static_cast<std::size_t>(total_tokens) * 64;
+    const unsigned convert_blocks = static_cast<unsigned>(elements / 256 + 1 < 148 * 8 ? elements / 256 + 1 : 148 * 8);
+    convert_dk_pe_kernel<<<convert_blocks, 256, 0, stream>>>(dk_pe, accumulator, elements);
+    CUDA_CHECK(cudaGetLastError());
 }
 
 void mla_compressed_attention_backward_cuda(__nv_bfloat16*, __nv_bfloat16*, __nv_bfloat16*, __nv_bfloat16*, const __nv_bfloat16*,
@@ -25,4 +822,5 @@ void mla_compressed_attention_backward_cuda(__nv_bfloat16*, __nv_bfloat16*, __nv
                                             const __nv_bfloat16*, const __nv_bfloat16*, int, int, int, int, int, float, cudaStream_t) {
     throw std::runtime_error("mla_compressed_attention_backward_cuda: not built yet");
 }
+
 }  // namespace dscuda

@@ -14,6 +14,11 @@ import torch
 from .library import checked, library  # noqa: F401 (re-exported for callers)
 
 
+# kernels one dscuda_mla_prefill_backward call launches (memset, delta pre-pass,
+# dQ kernel, dK/dV kernel, dk_pe conversion)
+PREFILL_BACKWARD_LAUNCHES = 5
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
