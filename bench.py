@@ -145,8 +145,18 @@ def run_ours(args, rank, world, device):
     from dscuda_b200 import mla
     from oracle import mla_oracle as oracle  # cpu_baseline leg only
 
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    for key in ("batch", "seq", "heads"):
+        if getattr(args, key) is not None:          # reduced sizes for profiler captures; the line names them
+            w[key] = getattr(args, key)
     peaks = measured_peaks()
+    if args.only_decode:
+        decode = bench_decode(mla, oracle, device, peaks, steps=args.steps, warmup=args.warmup, batch=args.decode_batch)
+        return {"metric": decode["metric"], "value": decode["value"], "unit": decode["unit"], "n_gpus": 1, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": decode["us_per_step"] / 1e3, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"decode only: batch {args.decode_batch}, heads 128, lengths uniform in [1024, 32768], seed 3"},
+                "gpu_launches": 2 * args.steps, "roofline": decode["roofline"], "decode": decode} if rank == 0 else None
     x = device_inputs(w, device)
     fwd_in = (x["q_nope"], x["q_pe"], x["k_nope"], x["k_pe"], x["v"])
     out = torch.empty_like(x["v"])
@@ -241,20 +251,20 @@ def run_ours(args, rank, world, device):
     return line
 
 
-def bench_decode(mla, oracle, device, peaks, steps=20, warmup=3, splits=16):
+def bench_decode(mla, oracle, device, peaks, steps=20, warmup=3, splits=16, batch=64):
     """Absorbed paged decode at batch 64, heads 128, lengths uniform in [1024, 32768] (seed 3)."""
-    query, cache, table, lengths = oracle.decode_inputs(seed=3, batch=64, heads=128)
+    query, cache, table, lengths = oracle.decode_inputs(seed=3, batch=batch, heads=128)
     total_tokens = int(lengths.sum())
     q, c, t, n = (z.to(device) for z in (query, cache, table, lengths))
-    workspace = mla.decode_workspace(64, 128, splits, 512, device)
-    out = torch.empty(64, 1, 128, 512, device=device, dtype=torch.bfloat16)
-    lse = torch.empty(64, 128, 1, device=device)
+    workspace = mla.decode_workspace(batch, 128, splits, 512, device)
+    out = torch.empty(batch, 1, 128, 512, device=device, dtype=torch.bfloat16)
+    lse = torch.empty(batch, 128, 1, device=device)
 
     def step():
         mla.mla_decode(q, c, t, n, SCALE, splits=splits, workspace=workspace, output=out, lse=lse)
 
     seconds = time_steps(step, steps, warmup, lambda: None) / steps
-    algorithmic = total_tokens * 576 * 2 + 64 * 128 * (576 + 512) * 2 + 64 * 128 * 4 + table.numel() * 4 + 64 * 4
+    algorithmic = total_tokens * 576 * 2 + batch * 128 * (576 + 512) * 2 + batch * 128 * 4 + table.numel() * 4 + batch * 4
     flops = 2 * (576 + 512) * 128 * total_tokens
     gbs = algorithmic / seconds / 1e9
     return {"metric": "absorbed MLA decode HBM GB/s", "value": gbs, "unit": "GB/s", "us_per_step": seconds * 1e6,
@@ -326,6 +336,11 @@ def main():
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--workload", default="train", choices=tuple(WORKLOADS))
+    parser.add_argument("--batch", type=int, default=None, help="override the workload's batch (profiler captures)")
+    parser.add_argument("--seq", type=int, default=None, help="override the workload's sequence length (profiler captures)")
+    parser.add_argument("--heads", type=int, default=None, help="override the workload's heads (profiler captures)")
+    parser.add_argument("--only-decode", action="store_true", help="time the paged decode alone")
+    parser.add_argument("--decode-batch", type=int, default=64)
     parser.add_argument("--skip-decode", action="store_true")
     parser.add_argument("--skip-cpu", action="store_true")
     args = parser.parse_args()

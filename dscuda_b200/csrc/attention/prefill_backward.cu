@@ -817,10 +817,4 @@ void mla_prefill_backward_cuda(__nv_bfloat16* dq, __nv_bfloat16* dk_nope, __nv_b
     CUDA_CHECK(cudaGetLastError());
 }
 
-void mla_compressed_attention_backward_cuda(__nv_bfloat16*, __nv_bfloat16*, __nv_bfloat16*, __nv_bfloat16*, const __nv_bfloat16*,
-                                            const __nv_bfloat16*, const float*, const __nv_bfloat16*, const __nv_bfloat16*,
-                                            const __nv_bfloat16*, const __nv_bfloat16*, int, int, int, int, int, float, cudaStream_t) {
-    throw std::runtime_error("mla_compressed_attention_backward_cuda: not built yet");
-}
-
 }  // namespace dscuda

@@ -90,6 +90,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Register re-distribution between warpgroups (all four warps of a warpgroup
+// must execute the same one).
+template <int REGISTERS>
+__device__ __forceinline__ void reg_alloc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGISTERS));
+}
+
+template <int REGISTERS>
+__device__ __forceinline__ void reg_dealloc() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGISTERS));
+}
+
 // ---------------------------------------------------------------------------
 // Proxy / tcgen05 fences
 // ---------------------------------------------------------------------------
@@ -260,6 +272,84 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
 
 __device__ __forceinline__ uint64_t make_kmajor_desc(uint32_t smem_addr) {
     return make_smem_desc(smem_addr, 16, 1024);
+}
+
+// Split form of the descriptor for issue loops: the high word is a compile-time
+// constant per operand kind, the low word is (address >> 4) | leading offset and
+// advances by (bytes >> 4) with a plain 32-bit add.
+__host__ __device__ constexpr uint32_t smem_desc_hi(uint32_t stride_bytes) {
+    return ((stride_bytes >> 4) & 0x3FFFU) | (1U << 14) | (2U << 29);
+}
+
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr, uint32_t leading_bytes) {
+    return ((smem_addr & 0x3FFFFU) >> 4) | (((leading_bytes >> 4) & 0x3FFFU) << 16);
+}
+
+__device__ __forceinline__ void mma_ss_split(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void mma_ts_split(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Packed fp32 pairs (sm_100): two FMAs / adds per instruction.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long ra;
+    asm("{\n\t"
+        ".reg .b64 x, y, z;\n\t"
+        "mov.b64 x, {%1, %2};\n\t"
+        "mov.b64 y, {%3, %4};\n\t"
+        "mov.b64 z, {%5, %6};\n\t"
+        "fma.rn.f32x2 %0, x, y, z;\n\t"
+        "}\n"
+        : "=l"(ra)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    float2 result;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(result.x), "=f"(result.y) : "l"(ra));
+    return result;
+}
+
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    unsigned long long ra;
+    asm("{\n\t"
+        ".reg .b64 x, y;\n\t"
+        "mov.b64 x, {%1, %2};\n\t"
+        "mov.b64 y, {%3, %4};\n\t"
+        "add.rn.f32x2 %0, x, y;\n\t"
+        "}\n"
+        : "=l"(ra)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    float2 result;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(result.x), "=f"(result.y) : "l"(ra));
+    return result;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float result;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(result) : "f"(a), "f"(b), "f"(c));
+    return result;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import functools
+import os
 import pathlib
 
 ROOT = pathlib.Path(__file__).resolve().parents[1]
@@ -34,7 +35,9 @@ FLASH_SYMBOLS = {
 
 
 def library_path(name: str) -> pathlib.Path:
-    return ROOT / "build" / f"libdscuda_{name}_bench.so"
+    """`build/` at the repository root, or the directory named by DSCUDA_BUILD_DIR."""
+    directory = pathlib.Path(os.environ["DSCUDA_BUILD_DIR"]) if os.environ.get("DSCUDA_BUILD_DIR") else ROOT / "build"
+    return directory / f"libdscuda_{name}_bench.so"
 
 
 @functools.lru_cache(maxsize=None)

@@ -83,3 +83,36 @@ def test_decode_rejects_bad_arguments(gpu):
     bad_pages = g["cache"].reshape(-1, 32, 1, 576).contiguous()
     with pytest.raises(RuntimeError, match="multiple of 64"):
         mla.mla_decode(g["query"].to(gpu), bad_pages.to(gpu), g["table"].to(gpu), g["lengths"].to(gpu), g["scale"])
+
+
+@pytest.mark.parametrize("name", ["b1_t1_h1", "b2_t17_h3", "b1_t65_h4"])
+def test_backward_matches_reference_fixture(gpu, name):
+    """Gradients against both things the reference compares with: its closed-form
+    mla_backward and autograd through its forward (benchmarks/mla.py:109-125)."""
+    from dscuda_b200 import mla
+    g = load_golden(f"absorbed_{name}")
+    inputs = [g[k].to(gpu) for k in ("query", "query_rope", "latent", "key_rope")]
+    grads = mla.mla_backward(g["dout"].to(gpu), g["out"].to(gpu), g["lse"].to(gpu), *inputs, g["scale"])
+    torch.cuda.synchronize()
+    for got, key in zip(grads, ("dquery", "dquery_rope", "dlatent", "dkey_rope")):
+        torch.testing.assert_close(got.cpu().float(), g[key].float(), atol=1e-2, rtol=1e-2)
+        torch.testing.assert_close(got.cpu().float(), g["ag_" + key].float(), atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("b,t,h", [(1, 128, 8), (2, 257, 4), (1, 512, 8), (2, 40, 16)])
+def test_backward_matches_oracle(gpu, b, t, h):
+    from conftest import rel_l2
+    from dscuda_b200 import mla
+    generator = torch.Generator().manual_seed(t * 3 + h)
+    shapes = ((b, t, h, 512), (b, t, h, 64), (b, t, 512), (b, t, 64))
+    inputs = [(torch.randn(s, generator=generator) * .25).bfloat16() for s in shapes]
+    dout = (torch.randn(b, t, h, 512, generator=generator) * .2).bfloat16()
+    scale = ctypes.c_float(576 ** -.5).value
+    device_inputs = [x.to(gpu) for x in inputs]
+    out, lse = mla.mla_forward(*device_inputs, scale)
+    grads = mla.mla_backward(dout.to(gpu), out, lse, *device_inputs, scale)
+    torch.cuda.synchronize()
+    reference = oracle.absorbed_backward(dout, out.cpu(), lse.cpu(), *inputs, scale, oracle.causal_mask(t))
+    for name, got, ref in zip(("dquery", "dquery_rope", "dlatent", "dkey_rope"), grads, reference):
+        assert rel_l2(got.cpu().float(), ref) <= 1e-2, name
+        torch.testing.assert_close(got.cpu().float(), ref.bfloat16().float(), atol=1e-2, rtol=1e-2)

@@ -1,0 +1,88 @@
+"""CPU-side checks of the C-ABI libraries: they load, they export every symbol
+the public header declares, and argument validation fails on the host with the
+reference's status/last-error convention (no GPU needed: a rejected call never
+reaches a launch)."""
+
+import ctypes
+import pathlib
+import re
+
+import pytest
+
+from dscuda_b200 import library
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "dscuda_c_api.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(dscuda_[a-z_]+)\s*\(", text)))
+
+
+def test_header_declares_the_reference_bridge_symbols():
+    names = declared_symbols()
+    # the five MLA symbols and two flash symbols the reference's harness binds
+    for required in ("dscuda_mla_last_error", "dscuda_mla_forward", "dscuda_mla_backward", "dscuda_mla_workspace_elements",
+                     "dscuda_mla_decode", "dscuda_flash_last_error", "dscuda_flash_forward"):
+        assert required in names
+
+
+def test_libraries_export_every_declared_symbol():
+    mla = ctypes.CDLL(str(library.library_path("mla")))
+    flash = ctypes.CDLL(str(library.library_path("flash_attention")))
+    for name in declared_symbols():
+        lib = flash if name.startswith("dscuda_flash") else mla
+        assert hasattr(lib, name), name
+    assert set(library.MLA_SYMBOLS) | set(library.FLASH_SYMBOLS) == set(declared_symbols())
+
+
+def test_workspace_sizes_are_host_only():
+    lib = library.library("mla")
+    # reference: kernels/attention/mla/sm89.cu:539-541 -> B*H*splits*(C+2)
+    assert lib.dscuda_mla_workspace_elements(64, 128, 8, 512) == 64 * 128 * 8 * 514
+    assert lib.dscuda_mla_prefill_backward_workspace_bytes(2, 8192, 16384, 128) >= 16384 * 64 * 4 + 16384 * 128 * 4
+
+
+@pytest.mark.parametrize("rank,rope", [(256, 64), (512, 32)])
+def test_absorbed_entry_points_reject_other_head_sizes(rank, rope):
+    lib = library.library("mla")
+    # reference: kernels/attention/mla/sm89.cu:20-24 -> invalid_argument -> status 1 + message
+    assert lib.dscuda_mla_forward(None, None, None, None, None, None, 1, 4, 2, rank, rope, 0.1, None) == 1
+    assert b"C=512 and RoPE=64" in lib.dscuda_mla_last_error()
+    assert lib.dscuda_mla_backward(*([None] * 11), 1, 4, 2, rank, rope, 0.1, None) == 1
+    assert b"C=512 and RoPE=64" in lib.dscuda_mla_last_error()
+    assert lib.dscuda_mla_decode(*([None] * 7), 1, 2, rank, rope, 64, 1, 8, 0.1, None) == 1
+    with pytest.raises(RuntimeError, match="C=512"):
+        library.checked(lib, "mla", 1)
+
+
+def test_prefill_entry_points_validate_on_the_host():
+    lib = library.library("mla")
+    args = [None] * 8
+    assert lib.dscuda_mla_prefill_forward(*args, 1, 16, 16, 2, 64, 64, 128, 0.1, None) == 1
+    assert b"nope=128" in lib.dscuda_mla_last_error()
+    assert lib.dscuda_mla_prefill_forward(*args, 1, 16, 17, 2, 128, 64, 128, 0.1, None) == 1
+    assert b"total_tokens" in lib.dscuda_mla_last_error()
+    assert lib.dscuda_mla_prefill_forward(*args, 1, 16, 16, 2, 128, 64, 128, -1.0, None) == 1
+    assert b"positive softmax scale" in lib.dscuda_mla_last_error()
+    assert lib.dscuda_mla_prefill_forward(*args, 1, 16, 16, 2, 128, 64, 128, 0.1, None) == 1
+    assert b"null tensor pointer" in lib.dscuda_mla_last_error()
+    assert lib.dscuda_mla_prefill_backward(*([None] * 14), 1, 16, 16, 2, 128, 64, 128, 0.1, None) == 1
+    assert b"null tensor pointer" in lib.dscuda_mla_last_error()
+
+
+def test_flash_entry_point_validates_on_the_host():
+    lib = library.library("flash_attention")
+    assert lib.dscuda_flash_forward(None, None, None, None, None, 1, 64, 4, 2, 64, 0.1, None) == 1
+    assert b"head_size 128" in lib.dscuda_flash_last_error()
+    assert lib.dscuda_flash_forward(None, None, None, None, None, 1, 64, 3, 2, 128, 0.1, None) == 1
+    assert b"divisible" in lib.dscuda_flash_last_error()
+
+
+def test_host_wrappers_refuse_cpu_tensors():
+    import torch
+    from dscuda_b200 import mla
+    x = torch.zeros(1, 4, 2, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        mla.flash_forward(x, x, x, 0.1)
