@@ -25,7 +25,9 @@
 #include "sm100_primitives.cuh"
 #include "../common/tensor_map.h"
 
+#include <mutex>
 #include <stdexcept>
+#include <string>
 
 namespace dscuda {
 namespace {
@@ -60,6 +62,14 @@ static_assert(Q_TMEM_CHUNKS * Q_CHUNK_BYTES <= STAGE_BYTES, "Q staging must fit 
 enum Mode : int { MODE_CAUSAL_PREFILL = 0, MODE_PAGED_DECODE = 1 };
 
 __device__ int absorbed_status = 0;
+
+// Scratch for mla_decode_forward_static_cuda: room for STATIC_DECODE_RECORDS
+// split partials of (maximum, sum, 512 outputs).  It lives in the image of the
+// library, so every GPU that loads the library keeps these 16.1 MiB until the
+// process ends.  The name below is only a host-side handle in host code; the
+// device address is looked up once per device with cudaGetSymbolAddress.
+constexpr std::size_t STATIC_DECODE_RECORDS = 8192;
+static __device__ __align__(256) float decode_static_scratch[STATIC_DECODE_RECORDS * (MLA_KV_RANK + 2)];
 
 struct AbsorbedParams {
     CUtensorMap q_lat;      // [rows, 512] box 128 x 64
@@ -735,6 +745,48 @@ void mla_decode_forward_cuda(__nv_bfloat16* output, float* logsumexp, const __nv
     CUDA_CHECK(cudaGetLastError());
     decode_combine_kernel<<<dim3(heads, batch_size), 128, 0, stream>>>(output, logsumexp, workspace, heads, splits);
     CUDA_CHECK(cudaGetLastError());
+}
+
+std::size_t mla_decode_static_capacity() {
+    return STATIC_DECODE_RECORDS;
+}
+
+void mla_decode_forward_static_cuda(__nv_bfloat16* output, float* logsumexp, const __nv_bfloat16* query,
+                                    const __nv_bfloat16* paged_kv_cache, const int* block_table, const int* cache_lengths, int batch_size,
+                                    int heads, int kv_rank, int rope_size, int page_size, int pages_per_sequence, int splits, float scale,
+                                    cudaStream_t stream) {
+    check_absorbed_shape(kv_rank, rope_size);
+    if (batch_size <= 0 || heads <= 0 || splits <= 0) {
+        throw std::invalid_argument("MLA decode requires positive batch, heads, pages and splits");
+    }
+    const unsigned long long records = static_cast<unsigned long long>(batch_size) * heads * splits;
+    if (records > STATIC_DECODE_RECORDS) {
+        throw std::invalid_argument("static-scratch MLA decode holds at most " + std::to_string(STATIC_DECODE_RECORDS) +
+                                    " split partials (batch*heads*splits = " + std::to_string(records) +
+                                    "); lower splits or use the entry point that takes a workspace");
+    }
+    // Device address of the scratch array, looked up once per device while that
+    // device is current.  The first call on a device does this set-up.
+    constexpr int MAX_DEVICES = 64;
+    static float* scratch_address[MAX_DEVICES] = {};
+    static std::mutex lock;
+    int device = 0;
+    CUDA_CHECK(cudaGetDevice(&device));
+    if (device < 0 || device >= MAX_DEVICES) {
+        throw std::runtime_error("static-scratch MLA decode supports device ordinals below 64");
+    }
+    float* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(lock);
+        if (scratch_address[device] == nullptr) {
+            void* address = nullptr;
+            CUDA_CHECK(cudaGetSymbolAddress(&address, decode_static_scratch));
+            scratch_address[device] = static_cast<float*>(address);
+        }
+        scratch = scratch_address[device];
+    }
+    mla_decode_forward_cuda(output, logsumexp, query, paged_kv_cache, block_table, cache_lengths, scratch, batch_size, heads, kv_rank,
+                            rope_size, page_size, pages_per_sequence, splits, scale, stream);
 }
 
 }  // namespace dscuda

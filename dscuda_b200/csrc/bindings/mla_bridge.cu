@@ -64,6 +64,19 @@ extern "C" int dscuda_mla_decode(bf16* output, float* lse, const bf16* query, co
     });
 }
 
+extern "C" std::size_t dscuda_mla_decode_static_capacity() {
+    return dscuda::mla_decode_static_capacity();
+}
+
+extern "C" int dscuda_mla_decode_static(bf16* output, float* lse, const bf16* query, const bf16* paged_cache, const int* block_table,
+                                        const int* lengths, int batch, int heads, int rank, int rope, int page_size, int pages,
+                                        int splits, float scale, cudaStream_t stream) {
+    return guarded([&] {
+        dscuda::mla_decode_forward_static_cuda(output, lse, query, paged_cache, block_table, lengths, batch, heads, rank, rope,
+                                               page_size, pages, splits, scale, stream);
+    });
+}
+
 extern "C" int dscuda_mla_prefill_forward(bf16* output, float* lse, const bf16* q_nope, const bf16* q_pe, const bf16* k_nope,
                                           const bf16* k_pe, const bf16* v, const int* cu_seqlens, int batch, int max_sequence,
                                           int total_tokens, int heads, int nope, int rope, int value, float scale,

@@ -51,6 +51,23 @@ int dscuda_mla_decode(
     int batch, int heads, int rank, int rope, int page_size, int pages, int splits,
     float scale, void* stream);
 
+/* No counterpart in the reference: paged decode that takes no workspace and
+ * allocates nothing.  For hosts that cannot allocate device memory where they
+ * call from (fixed up-front memory pools, plugins inside a foreign allocator,
+ * places where cudaMalloc would stall the device).  The split partials live in a
+ * fixed 16.1 MiB array inside the library; batch*heads*splits may be at most
+ * dscuda_mla_decode_static_capacity() (8192), else status 1.  The first call on
+ * a device resolves the array's address and should happen outside stream
+ * capture.  All calls on a device share the array: calls that overlap on the
+ * GPU race, so keep them in one stream order. */
+size_t dscuda_mla_decode_static_capacity(void);
+int dscuda_mla_decode_static(
+    void* output, float* lse,
+    const void* query, const void* paged_cache,
+    const int* block_table, const int* lengths,
+    int batch, int heads, int rank, int rope, int page_size, int pages, int splits,
+    float scale, void* stream);
+
 /* No counterpart in the reference: non-absorbed causal prefill forward
  * (include/mla.h, mla_prefill_forward_cuda).  cu_seqlens may be NULL (dense). */
 int dscuda_mla_prefill_forward(

@@ -96,6 +96,45 @@ void mla_decode_forward_cuda(
     float scale,
     cudaStream_t stream = nullptr);
 
+// Paged decode for callers that cannot hand over a workspace (no counterpart in
+// the reference).  Same arguments and results as mla_decode_forward_cuda minus
+// `workspace`: the split partials go to a fixed array inside the library image
+// instead.  It is meant for hosts that may not allocate device memory at the
+// point of the call - a serving loop whose memory pool is sized up front and
+// handed out in full, a plugin that runs inside someone else's allocator, code
+// that runs where cudaMalloc would stall every stream on the device.  Nothing
+// is allocated or freed here, by CUDA or by any library.
+//
+// Limits and rules:
+//   * batch_size * heads * splits must not exceed mla_decode_static_capacity()
+//     (8192 partials, 16.1 MiB held by every GPU that loads the library, until
+//     the process exits); larger requests throw std::invalid_argument.
+//   * The first call on each device looks up the array's device address
+//     (cudaGetSymbolAddress with that device current).  Make that first call
+//     outside any stream capture.
+//   * Every call on a device uses the same array.  Nothing in it has to be
+//     cleared between calls (each call rewrites every partial it later reads),
+//     but two calls that overlap on the GPU - different streams, or graphs
+//     replayed side by side - race on it.  Serialise them.
+std::size_t mla_decode_static_capacity();
+
+void mla_decode_forward_static_cuda(
+    __nv_bfloat16* output,
+    float* logsumexp,
+    const __nv_bfloat16* query,
+    const __nv_bfloat16* paged_kv_cache,
+    const int* block_table,
+    const int* cache_lengths,
+    int batch_size,
+    int heads,
+    int kv_rank,
+    int rope_size,
+    int page_size,
+    int pages_per_sequence,
+    int splits,
+    float scale,
+    cudaStream_t stream = nullptr);
+
 // ---------------------------------------------------------------------------
 // Non-absorbed causal prefill / training path (no counterpart in the reference).
 //
