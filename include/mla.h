@@ -114,8 +114,8 @@ void mla_decode_forward_cuda(
 //     outside any stream capture.
 //   * Every call on a device uses the same array.  Nothing in it has to be
 //     cleared between calls (each call rewrites every partial it later reads),
-//     but two calls that overlap on the GPU - different streams, or graphs
-//     replayed side by side - race on it.  Serialise them.
+//     but two calls that overlap on the GPU (for example on different
+//     streams) race on it.  Serialise them.
 std::size_t mla_decode_static_capacity();
 
 void mla_decode_forward_static_cuda(
