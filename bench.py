@@ -222,8 +222,8 @@ def run_ours(args, rank, world, device):
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     seconds, e2e_seconds = float(times[0]), float(times[1])
 
-    decode = bench_decode(mla, oracle, device, peaks) if rank == 0 and not args.skip_decode else None
-    cpu = cpu_baseline(oracle, 12.0) if rank == 0 and not args.skip_cpu else None
+    decode = bench_decode(mla, oracle, device, peaks) if world == 1 and not args.skip_decode else None
+    cpu = cpu_baseline(oracle, 12.0) if world == 1 and not args.skip_cpu else None
 
     if rank != 0:
         return None
