@@ -7,15 +7,20 @@
 //     each row sees keys 0..its token;
 //   * paged split-KV decode (mla_decode_forward_cuda): the 128 rows are the
 //     heads of one sequence's single query token, keys come from 64-token tiles
-//     of the paged cache found through the block table, and each CTA writes an
-//     unnormalised partial (max, sum, output) that a second kernel merges.
+//     of the paged cache found through the block table, and each piece of work
+//     writes an unnormalised partial (max, sum, output) that a second kernel
+//     merges.  The decode grid is persistent: one CTA per SM, in pairs, and the
+//     key tiles of all sequences are dealt to the pairs in equal ranges.
 //
 // A 128x512 fp32 output tile would fill all of tensor memory, so a tile is
 // handled by two CTAs: both compute S = Q K^T (K = 576) and each accumulates
-// one 256-column half of O = P V.  Tensor memory per CTA: O 256 columns, two S
-// buffers of 64 columns (P overwrites S in place as bf16), and 128 columns that
-// hold the first 256 columns of Q as an MMA A operand, which leaves shared
-// memory for the remaining Q columns (80 KB) and two 72 KB key-tile stages.
+// one 256-column half of O = P V.  Tensor memory per CTA: O 256 columns, S 64
+// columns (P overwrites it in place as bf16), and 192 columns that hold the
+// first 384 columns of Q as an MMA A operand.  That leaves shared memory for
+// the other 192 Q columns (48 KB) and two rings of key chunks: the five 8 KB
+// chunks of a tile that only S needs (ring of 2 tiles) and the four that are
+// also this CTA's V (ring of 3 tiles).  The first ring is released as soon as
+// S is computed, the second after P V, so loads run two to three tiles ahead.
 //
 // Warps 0-3: softmax / epilogue (one thread per row); warp 4: MMA issue;
 // warp 5: TMA loads.  All waits are bounded.
@@ -25,6 +30,7 @@
 #include "sm100_primitives.cuh"
 #include "../common/tensor_map.h"
 
+#include <algorithm>
 #include <mutex>
 #include <stdexcept>
 #include <string>
@@ -41,23 +47,31 @@ constexpr int ROPE = MLA_ROPE_SIZE;             // 64
 constexpr int WIDTH = RANK + ROPE;              // 576
 constexpr int CHUNKS = WIDTH / 64;              // 9 column chunks of 64
 constexpr int HALF_V = RANK / 2;                // value columns per CTA
-constexpr int Q_TMEM_CHUNKS = 4;                // Q columns 0..255 live in tensor memory
+constexpr int Q_TMEM_CHUNKS = 6;                // Q columns 0..383 live in tensor memory
 constexpr int Q_SMEM_CHUNKS = CHUNKS - Q_TMEM_CHUNKS;
 constexpr int Q_CHUNK_BYTES = ROWS * 128;       // 16 KB
 constexpr int K_CHUNK_BYTES = KEYS * 128;       // 8 KB
-constexpr int STAGE_BYTES = CHUNKS * K_CHUNK_BYTES;          // 72 KB
-constexpr int Q_SMEM_BYTES = Q_SMEM_CHUNKS * Q_CHUNK_BYTES;  // 80 KB
+constexpr int A_CHUNKS = 5;                     // key chunks of a tile that only S needs
+constexpr int B_CHUNKS = 4;                     // key chunks of a tile that are also this CTA's V
+constexpr int A_UNIT_BYTES = A_CHUNKS * K_CHUNK_BYTES;       // 40 KB
+constexpr int B_UNIT_BYTES = B_CHUNKS * K_CHUNK_BYTES;       // 32 KB
+constexpr int A_SLOTS = 2;
+constexpr int B_SLOTS = 3;
+constexpr int Q_SMEM_BYTES = Q_SMEM_CHUNKS * Q_CHUNK_BYTES;  // 48 KB
+constexpr int A_RING_BYTES = A_SLOTS * A_UNIT_BYTES;         // 80 KB
+constexpr int B_RING_BYTES = B_SLOTS * B_UNIT_BYTES;         // 96 KB
 constexpr int MISC_BYTES = 1024;
-constexpr int SMEM_BYTES = Q_SMEM_BYTES + 2 * STAGE_BYTES + MISC_BYTES + 1024;
+constexpr int SMEM_BYTES = Q_SMEM_BYTES + A_RING_BYTES + B_RING_BYTES + MISC_BYTES + 1024;
 constexpr int THREADS = 192;
 constexpr int MMA_WARP = 4;
 constexpr int LOAD_WARP = 5;
 constexpr int TMEM_COLUMNS = 512;
 constexpr int TMEM_O = 0;                       // 256 columns
-constexpr int TMEM_S = 256;                     // 2 x 64 columns
-constexpr int TMEM_Q = 384;                     // 128 columns = 4 chunks x 32
+constexpr int TMEM_S = 256;                     // 64 columns
+constexpr int TMEM_Q = 320;                     // 192 columns = 6 chunks x 32
 constexpr float RESCALE_THRESHOLD = 8.0F;
-static_assert(Q_TMEM_CHUNKS * Q_CHUNK_BYTES <= STAGE_BYTES, "Q staging must fit in one key stage");
+static_assert(Q_TMEM_CHUNKS * Q_CHUNK_BYTES <= B_RING_BYTES, "Q staging must fit in the value ring");
+static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 
 enum Mode : int { MODE_CAUSAL_PREFILL = 0, MODE_PAGED_DECODE = 1 };
 
@@ -92,24 +106,132 @@ struct AbsorbedParams {
     float scale_log2;
 #ifdef DSCUDA_DEBUG_DUMP
     float* debug;           // [128*64 raw S of the first tile][128*258 unnormalised O half, l, m] of CTA (0,0,0)
+    long long* stamps;      // clock64 samples of CTA 0: [role 0..2][tile][8]
 #endif
 };
 
+#ifdef DSCUDA_DEBUG_DUMP
+#define STAMP(role, iteration, slot)                                                                         \
+    do {                                                                                                     \
+        if (p.stamps != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (iteration) < 64) { \
+            p.stamps[((role) * 64 + (iteration)) * 8 + (slot)] = clock64();                                 \
+        }                                                                                                    \
+    } while (0)
+#else
+#define STAMP(role, iteration, slot) do { } while (0)
+#endif
+
+struct Schedule {
+    int chunk;          // 64-key tiles per CTA pair (range scheme)
+    int total;          // tiles of all units
+    int first_unit;     // first unit that overlaps this pair's range
+    int first_offset;   // global tile index at which that unit starts
+};
+
 struct AbsorbedBarriers {
-    uint64_t q_full;            // Q chunks that stay in shared memory
+    uint64_t q_full;            // Q chunks that stay in shared memory (one phase per segment)
     uint64_t q_stage_full;      // Q chunks on their way to tensor memory
     uint64_t q_tmem_ready;      // 128 arrivals: those chunks are in tensor memory
-    uint64_t full_a[2];         // per stage: the five key chunks only S needs
-    uint64_t full_b[2];         // per stage: the four chunks that are also this CTA's V
-    uint64_t empty_a[2];
-    uint64_t empty_b[2];
-    uint64_t s_full[2];
-    uint64_t p_full[2];
-    uint64_t o_done;            // one completion per P V
+    uint64_t full_a[A_SLOTS];   // ring of the five key chunks only S needs
+    uint64_t empty_a[A_SLOTS];
+    uint64_t full_b[B_SLOTS];   // ring of the four chunks that are also this CTA's V
+    uint64_t empty_b[B_SLOTS];
+    uint64_t s_full;            // one phase per tile
+    uint64_t p_full;            // one phase per tile
+    uint64_t o_final;           // one phase per segment: the last P V has finished
     uint32_t tmem_base;
     int abort_flag;
+    Schedule schedule;
 };
 static_assert(sizeof(AbsorbedBarriers) <= MISC_BYTES, "barrier block too large");
+
+// One piece of work: tiles [tile_begin, tile_end) of the keys visible to the 128
+// rows `row_tile` of sequence `b`.
+struct Segment {
+    int b;
+    int row_tile;
+    int tile_begin;
+    int tile_end;
+    int slot;            // decode: which partial record of (b, head) this segment fills
+    bool last_of_unit;   // decode: the segment that reaches the end of the sequence
+};
+
+// Walks the segments of this CTA.  Every role thread runs its own walker over the
+// same schedule, so all roles see the same sequence of segments.
+//
+// Decode units are (sequence, 128-head tile) pairs, laid end to end as one long
+// list of 64-key tiles.  With splits > 1 the list is cut into equal ranges, one
+// per CTA pair, so every pair streams about the same number of cache bytes
+// whatever the sequence lengths are; a unit cut by a range boundary produces one
+// partial per range it touches.  The range length is never smaller than
+// ceil(longest unit / (splits - 1)), which bounds the partials of a unit by
+// `splits`.  With splits == 1 whole units are dealt round-robin.
+struct Walker {
+    int unit;
+    int offset;     // global tile index where `unit` starts
+    bool done;
+};
+
+__device__ __forceinline__ int unit_tiles(const AbsorbedParams& p, int unit, int head_tiles) {
+    return (p.lengths[unit / head_tiles] + KEYS - 1) / KEYS;
+}
+
+__device__ __forceinline__ bool next_segment(const AbsorbedParams& p, const Schedule& s, Walker& w, Segment& seg, int pair, int pairs) {
+    if (w.done) {
+        return false;
+    }
+    if (p.mode == MODE_CAUSAL_PREFILL) {
+        const int rows_total = p.sequence * p.heads;
+        const int first = (blockIdx.y >> 1) * ROWS;
+        const int last_token = (min(first + ROWS, rows_total) - 1) / p.heads;
+        seg.b = blockIdx.z;
+        seg.row_tile = blockIdx.y >> 1;
+        seg.tile_begin = 0;
+        seg.tile_end = last_token / KEYS + 1;
+        seg.slot = 0;
+        seg.last_of_unit = true;
+        w.done = true;
+        return true;
+    }
+    const int head_tiles = (p.heads + ROWS - 1) / ROWS;
+    const int units = p.batch * head_tiles;
+    if (p.splits == 1) {
+        if (w.unit >= units) {
+            w.done = true;
+            return false;
+        }
+        seg.b = w.unit / head_tiles;
+        seg.row_tile = w.unit % head_tiles;
+        seg.tile_begin = 0;
+        seg.tile_end = unit_tiles(p, w.unit, head_tiles);
+        seg.slot = 0;
+        seg.last_of_unit = true;
+        w.unit += pairs;
+        return true;
+    }
+    const long long lo = static_cast<long long>(pair) * s.chunk;
+    const long long hi = min(lo + s.chunk, static_cast<long long>(s.total));
+    while (w.unit < units && w.offset < hi) {
+        const int tiles = unit_tiles(p, w.unit, head_tiles);
+        const int begin = static_cast<int>(max(lo, static_cast<long long>(w.offset)) - w.offset);
+        const int end = static_cast<int>(min(hi, static_cast<long long>(w.offset) + tiles) - w.offset);
+        const int unit = w.unit;
+        const int offset = w.offset;
+        w.unit += 1;
+        w.offset += tiles;
+        if (end > begin) {
+            seg.b = unit / head_tiles;
+            seg.row_tile = unit % head_tiles;
+            seg.tile_begin = begin;
+            seg.tile_end = end;
+            seg.slot = pair - offset / s.chunk;
+            seg.last_of_unit = end == tiles;
+            return true;
+        }
+    }
+    w.done = true;
+    return false;
+}
 
 __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __grid_constant__ AbsorbedParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -118,77 +240,71 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
     }
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
-    const int half = blockIdx.y & 1;            // which 256 value columns
-    const int row_tile = blockIdx.y >> 1;
-    const int b = blockIdx.z;
-
-    // ---- work description --------------------------------------------------
-    int q_row0;          // first row of the Q tile in the 2-D Q view
-    int valid_rows;      // rows of the tile that exist
-    int tile_begin;      // first 64-key tile
-    int tile_end;        // one past the last
-    int kv_end;          // keys >= kv_end are never visible to this CTA
-    int min_limit;       // smallest per-row key limit; tiles past it need masking
-    int split = 0;
-    if (p.mode == MODE_CAUSAL_PREFILL) {
-        const int rows_total = p.sequence * p.heads;
-        const int first = row_tile * ROWS;
-        q_row0 = b * rows_total + first;
-        valid_rows = min(ROWS, rows_total - first);
-        const int last_token = (first + valid_rows - 1) / p.heads;
-        kv_end = last_token + 1;
-        min_limit = first / p.heads + 1;
-        tile_begin = 0;
-        tile_end = (kv_end + KEYS - 1) / KEYS;
-    } else {
-        split = blockIdx.x;
-        const int first = row_tile * ROWS;
-        q_row0 = b * p.heads + first;
-        valid_rows = min(ROWS, p.heads - first);
-        const int length = p.lengths[b];
-        const int tiles_total = (length + KEYS - 1) / KEYS;
-        const int per_split = (tiles_total + p.splits - 1) / p.splits;
-        tile_begin = min(split * per_split, tiles_total);
-        tile_end = min(tile_begin + per_split, tiles_total);
-        kv_end = min(length, tile_end * KEYS);
-        min_limit = kv_end;
-    }
-    const int tile_count = tile_end - tile_begin;
-
-    if (tile_count <= 0) {
-        // An empty split still owns a partial slot: mark it as carrying no weight.
-        if (p.mode == MODE_PAGED_DECODE && half == 0 && threadIdx.x < valid_rows) {
-            const int head = row_tile * ROWS + threadIdx.x;
-            float* record = p.workspace + ((static_cast<size_t>(b) * p.heads + head) * p.splits + split) * (RANK + 2);
-            record[0] = -INFINITY;
-            record[1] = 0.0F;
-        }
-        return;
-    }
+    // prefill: grid (1, 2*row_tiles, B); decode: grid (2*pairs, 1, 1)
+    const bool decode = p.mode == MODE_PAGED_DECODE;
+    const int half = decode ? (blockIdx.x & 1) : (blockIdx.y & 1);      // which 256 value columns
+    const int pair = decode ? (blockIdx.x >> 1) : 0;
+    const int pairs = decode ? (gridDim.x >> 1) : 1;
 
     // ---- shared memory ------------------------------------------------------
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023U) & ~1023U;
     uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t q_smem = smem_base;
-    const uint32_t stage_smem = smem_base + Q_SMEM_BYTES;
-    AbsorbedBarriers* bars = reinterpret_cast<AbsorbedBarriers*>(smem_aligned + Q_SMEM_BYTES + 2 * STAGE_BYTES);
+    const uint32_t a_ring = smem_base + Q_SMEM_BYTES;
+    const uint32_t b_ring = a_ring + A_RING_BYTES;
+    uint8_t* b_ring_ptr = smem_aligned + Q_SMEM_BYTES + A_RING_BYTES;
+    AbsorbedBarriers* bars = reinterpret_cast<AbsorbedBarriers*>(smem_aligned + Q_SMEM_BYTES + A_RING_BYTES + B_RING_BYTES);
     volatile int* abort_flag = &bars->abort_flag;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bars->q_full), 1);
         mbar_init(smem_u32(&bars->q_stage_full), 1);
         mbar_init(smem_u32(&bars->q_tmem_ready), ROWS);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < A_SLOTS; ++i) {
             mbar_init(smem_u32(&bars->full_a[i]), 1);
-            mbar_init(smem_u32(&bars->full_b[i]), 1);
             mbar_init(smem_u32(&bars->empty_a[i]), 1);
-            mbar_init(smem_u32(&bars->empty_b[i]), 1);
-            mbar_init(smem_u32(&bars->s_full[i]), 1);
-            mbar_init(smem_u32(&bars->p_full[i]), ROWS);
         }
-        mbar_init(smem_u32(&bars->o_done), 1);
+        for (int i = 0; i < B_SLOTS; ++i) {
+            mbar_init(smem_u32(&bars->full_b[i]), 1);
+            mbar_init(smem_u32(&bars->empty_b[i]), 1);
+        }
+        mbar_init(smem_u32(&bars->s_full), 1);
+        mbar_init(smem_u32(&bars->p_full), ROWS);
+        mbar_init(smem_u32(&bars->o_final), 1);
         bars->abort_flag = 0;
         mbar_init_fence();
+        // ---- schedule of this pair (decode with splits > 1) -------------------
+        Schedule schedule = {1, 0, 0, 0};
+        if (decode && p.splits > 1) {
+            const int head_tiles = (p.heads + ROWS - 1) / ROWS;
+            long long total = 0;
+            int longest = 0;
+            for (int b = 0; b < p.batch; ++b) {
+                const int tiles = (p.lengths[b] + KEYS - 1) / KEYS;
+                total += static_cast<long long>(tiles) * head_tiles;
+                longest = max(longest, tiles);
+            }
+            long long chunk = (total + pairs - 1) / pairs;
+            chunk = max(chunk, static_cast<long long>((longest + p.splits - 2) / (p.splits - 1)));
+            chunk = max(chunk, 1LL);
+            schedule.chunk = static_cast<int>(min(chunk, 0x7fffffffLL));
+            schedule.total = static_cast<int>(min(total, 0x7fffffffLL));
+            const long long lo = static_cast<long long>(pair) * schedule.chunk;
+            int unit = 0;
+            long long offset = 0;
+            const int units = p.batch * head_tiles;
+            while (unit < units) {
+                const int tiles = unit_tiles(p, unit, head_tiles);
+                if (offset + tiles > lo) {
+                    break;
+                }
+                offset += tiles;
+                ++unit;
+            }
+            schedule.first_unit = unit;
+            schedule.first_offset = static_cast<int>(offset);
+        }
+        bars->schedule = schedule;
     }
     if (warp == MMA_WARP) {
         tmem_alloc(smem_u32(&bars->tmem_base), TMEM_COLUMNS);
@@ -204,131 +320,214 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+    const Schedule schedule = bars->schedule;
 
-    // first and last (exclusive) chunk of a stage that doubles as this CTA's V
+    // Key chunk c holds columns 64c..64c+63 (c = 8: the rotary columns).  Chunks
+    // v_first..v_first+3 are this CTA's V ("B" group); the other five are the "A" group.
+    // Six Q chunks sit in tensor memory (the B group's four and two of the A group),
+    // three in shared memory.  Inside a tile the three shared-memory slices are issued
+    // first and the six tensor-memory slices after them: an A-from-shared-memory MMA
+    // that follows A-from-tensor-memory MMAs on the same accumulator costs about three
+    // times its normal issue time, the other order costs nothing.
     const int v_first = half * 4;
+    //   A-group order: half 0 -> 6,7,8,4,5   half 1 -> 2,3,8,0,1   (first three: Q in shared memory)
+    auto a_chunk = [&](int i) -> int {
+        const int table0[A_CHUNKS] = {6, 7, 8, 4, 5};
+        const int table1[A_CHUNKS] = {2, 3, 8, 0, 1};
+        return half == 0 ? table0[i] : table1[i];
+    };
+    // tensor-memory slot t (0..5) holds Q chunk: half 0 -> t, half 1 -> 0,1,4,5,6,7
+    auto tmem_chunk = [&](int t) -> int { return half == 0 ? t : (t < 2 ? t : t + 2); };
+    // slots of the A group's two tensor-memory slices and of the B group's four
+    const int a_ts_slot = half == 0 ? 4 : 0;
+    const int b_ts_slot = half == 0 ? 0 : 2;
+
+    Walker walker;
+    walker.unit = (decode && p.splits == 1) ? pair : schedule.first_unit;
+    walker.offset = schedule.first_offset;
+    walker.done = false;
+    Segment seg;
+    int segment_index = 0;      // segments this CTA has started (every role counts the same)
+    int tile_index = 0;         // key tiles this CTA has started, over all segments
 
     if (warp == LOAD_WARP) {
         // =================== TMA producer ===================================
-        if (lane == 0) {
-            // Q columns 256..575 stay in shared memory.
-            {
-                const uint32_t bar = smem_u32(&bars->q_full);
-                mbar_arrive_expect_tx(bar, Q_SMEM_BYTES);
-                for (int c = 0; c < Q_SMEM_CHUNKS; ++c) {
-                    const int chunk = Q_TMEM_CHUNKS + c;
-                    if (chunk < 8) {
-                        tma_load_2d(q_smem + c * Q_CHUNK_BYTES, &p.q_lat, bar, chunk * 64, q_row0);
-                    } else {
-                        tma_load_2d(q_smem + c * Q_CHUNK_BYTES, &p.q_rope, bar, 0, q_row0);
+        // All 32 lanes walk the loop (they prefetch block-table entries, one tile
+        // per lane); lane 0 waits on barriers and issues the loads.
+        bool alive = true;
+        while (alive && next_segment(p, schedule, walker, seg, pair, pairs)) {
+            const int tile_count = seg.tile_end - seg.tile_begin;
+            const int q_row0 = decode ? seg.b * p.heads + seg.row_tile * ROWS : seg.b * p.sequence * p.heads + seg.row_tile * ROWS;
+            const uint32_t seg_parity = segment_index & 1;
+            if (lane == 0) {
+                // Q is staged through the value ring and (three chunks) kept in shared
+                // memory: every tile issued so far must have finished its P V.
+                for (int back = 1; back <= B_SLOTS && alive; ++back) {
+                    const int tile = tile_index - back;
+                    if (tile >= 0) {
+                        alive = mbar_wait(smem_u32(&bars->empty_b[tile % B_SLOTS]), (tile / B_SLOTS) & 1, abort_flag, &absorbed_status);
+                    }
+                }
+                if (alive) {
+                    const uint32_t bar = smem_u32(&bars->q_full);
+                    mbar_arrive_expect_tx(bar, Q_SMEM_BYTES);
+                    for (int c = 0; c < Q_SMEM_CHUNKS; ++c) {
+                        const int chunk = a_chunk(c);
+                        if (chunk < 8) {
+                            tma_load_2d(q_smem + c * Q_CHUNK_BYTES, &p.q_lat, bar, chunk * 64, q_row0);
+                        } else {
+                            tma_load_2d(q_smem + c * Q_CHUNK_BYTES, &p.q_rope, bar, 0, q_row0);
+                        }
+                    }
+                    const uint32_t stage_bar = smem_u32(&bars->q_stage_full);
+                    mbar_arrive_expect_tx(stage_bar, Q_TMEM_CHUNKS * Q_CHUNK_BYTES);
+                    for (int c = 0; c < Q_TMEM_CHUNKS; ++c) {
+                        tma_load_2d(b_ring + c * Q_CHUNK_BYTES, &p.q_lat, stage_bar, tmem_chunk(c) * 64, q_row0);
                     }
                 }
             }
-            // Q columns 0..255 pass through stage 1 on their way to tensor memory.
-            {
-                const uint32_t bar = smem_u32(&bars->q_stage_full);
-                mbar_arrive_expect_tx(bar, Q_TMEM_CHUNKS * Q_CHUNK_BYTES);
-                for (int c = 0; c < Q_TMEM_CHUNKS; ++c) {
-                    tma_load_2d(stage_smem + STAGE_BYTES + c * Q_CHUNK_BYTES, &p.q_lat, bar, c * 64, q_row0);
-                }
-            }
-            bool alive = true;
+            alive = __shfl_sync(0xffffffffU, alive ? 1 : 0, 0) != 0;
+            int table_entry = 0;
             for (int j = 0; j < tile_count && alive; ++j) {
-                const int stage = j & 1;
-                if (j == 1) {
-                    alive = mbar_wait(smem_u32(&bars->q_tmem_ready), 0, abort_flag, &absorbed_status);
-                } else if (j >= 2) {
-                    const uint32_t parity = ((j >> 1) - 1) & 1;
-                    alive = mbar_wait(smem_u32(&bars->empty_a[stage]), parity, abort_flag, &absorbed_status) &&
-                            mbar_wait(smem_u32(&bars->empty_b[stage]), parity, abort_flag, &absorbed_status);
+                const int token = (seg.tile_begin + j) * KEYS;
+                if (decode && (j & 31) == 0) {
+                    // one block-table entry per lane for the next 32 tiles
+                    const int ahead = token + lane * KEYS;
+                    table_entry = ahead < seg.tile_end * KEYS
+                                      ? __ldg(p.block_table + static_cast<size_t>(seg.b) * p.pages + ahead / p.page_size)
+                                      : 0;
                 }
-                if (!alive) {
-                    break;
-                }
-                const int token = (tile_begin + j) * KEYS;
-                int y;
-                if (p.mode == MODE_CAUSAL_PREFILL) {
-                    y = b * p.sequence + token;
-                } else {
-                    const int page = token / p.page_size;
-                    y = __ldg(p.block_table + static_cast<size_t>(b) * p.pages + page) * p.page_size + token % p.page_size;
-                }
-                const uint32_t bar_a = smem_u32(&bars->full_a[stage]);
-                const uint32_t bar_b = smem_u32(&bars->full_b[stage]);
-                mbar_arrive_expect_tx(bar_a, 5 * K_CHUNK_BYTES);
-                mbar_arrive_expect_tx(bar_b, 4 * K_CHUNK_BYTES);
-                const uint32_t dst = stage_smem + stage * STAGE_BYTES;
-                for (int c = 0; c < CHUNKS; ++c) {
-                    const bool is_v = c >= v_first && c < v_first + 4;
-                    const uint32_t bar = is_v ? bar_b : bar_a;
-                    if (c < 8) {
-                        tma_load_2d(dst + c * K_CHUNK_BYTES, &p.k_lat, bar, c * 64, y);
-                    } else {
-                        tma_load_2d(dst + c * K_CHUNK_BYTES, &p.k_rope, bar, 0, y);
+                const int physical_page = __shfl_sync(0xffffffffU, table_entry, j & 31);
+                if (lane == 0) {
+                    const int tile = tile_index + j;
+                    const int y = decode ? physical_page * p.page_size + token % p.page_size : seg.b * p.sequence + token;
+                    // "A" group: free once the S of two tiles ago has been computed
+                    const int slot_a = tile % A_SLOTS;
+                    if (tile >= A_SLOTS) {
+                        alive = mbar_wait(smem_u32(&bars->empty_a[slot_a]), (tile / A_SLOTS - 1) & 1, abort_flag, &absorbed_status);
+                    }
+                    if (alive) {
+                        STAMP(2, tile, 0);
+                        const uint32_t bar = smem_u32(&bars->full_a[slot_a]);
+                        mbar_arrive_expect_tx(bar, A_UNIT_BYTES);
+                        for (int i = 0; i < A_CHUNKS; ++i) {
+                            const int c = a_chunk(i);
+                            const uint32_t dst = a_ring + slot_a * A_UNIT_BYTES + i * K_CHUNK_BYTES;
+                            if (c < 8) {
+                                tma_load_2d(dst, &p.k_lat, bar, c * 64, y);
+                            } else {
+                                tma_load_2d(dst, &p.k_rope, bar, 0, y);
+                            }
+                        }
+                    }
+                    // "B" group: the first tile of a segment waits for the Q staging to be
+                    // consumed, later ones for the P V of three tiles ago
+                    const int slot_b = tile % B_SLOTS;
+                    if (alive && j == 0) {
+                        alive = mbar_wait(smem_u32(&bars->q_tmem_ready), seg_parity, abort_flag, &absorbed_status);
+                    } else if (alive && j >= B_SLOTS) {
+                        alive = mbar_wait(smem_u32(&bars->empty_b[slot_b]), (tile / B_SLOTS - 1) & 1, abort_flag, &absorbed_status);
+                    }
+                    if (alive) {
+                        STAMP(2, tile, 1);
+                        const uint32_t bar = smem_u32(&bars->full_b[slot_b]);
+                        mbar_arrive_expect_tx(bar, B_UNIT_BYTES);
+                        for (int i = 0; i < B_CHUNKS; ++i) {
+                            tma_load_2d(b_ring + slot_b * B_UNIT_BYTES + i * K_CHUNK_BYTES, &p.k_lat, bar, (v_first + i) * 64, y);
+                        }
                     }
                 }
+                alive = __shfl_sync(0xffffffffU, alive ? 1 : 0, 0) != 0;
             }
+            tile_index += tile_count;
+            segment_index += 1;
         }
     } else if (warp == MMA_WARP) {
         // =================== MMA issuer =====================================
         if (lane == 0) {
             constexpr uint32_t IDESC_QK = make_idesc_bf16(ROWS, KEYS, false, false);
             constexpr uint32_t IDESC_PV = make_idesc_bf16(ROWS, HALF_V, false, true);
-            bool alive = mbar_wait(smem_u32(&bars->q_full), 0, abort_flag, &absorbed_status) &&
-                         mbar_wait(smem_u32(&bars->q_tmem_ready), 0, abort_flag, &absorbed_status);
-            auto issue_qk = [&](int j) {
-                const int stage = j & 1;
-                const uint32_t parity = (j >> 1) & 1;
-                alive = mbar_wait(smem_u32(&bars->full_a[stage]), parity, abort_flag, &absorbed_status) &&
-                        mbar_wait(smem_u32(&bars->full_b[stage]), parity, abort_flag, &absorbed_status);
-                if (!alive) {
-                    return;
-                }
-                tc_fence_after_sync();
-                const uint32_t d = tmem_base + TMEM_S + stage * KEYS;
-                const uint32_t k_stage = stage_smem + stage * STAGE_BYTES;
+            constexpr uint32_t HI = smem_desc_hi(1024);
+            constexpr uint32_t CHUNK_LO = K_CHUNK_BYTES >> 4;
+            const uint32_t q_lo = smem_desc_lo(q_smem, 16);
+            const uint32_t a_lo = smem_desc_lo(a_ring, 16);
+            const uint32_t b_lo = smem_desc_lo(b_ring, 16);
+            const uint32_t v_lo = smem_desc_lo(b_ring, K_CHUNK_BYTES);
+            const uint32_t s_tmem = tmem_base + TMEM_S;
+            bool alive = true;
+            // one 64-column slice of the 576-deep contraction against the key chunk at k_lo:
+            // Q from shared-memory chunk `index` (shared == true) or tensor-memory slot `index`
+            auto issue_slice = [&](bool shared, int index, uint32_t k_lo, bool first) {
 #pragma unroll
-                for (int c = 0; c < CHUNKS; ++c) {
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const uint64_t k_desc = make_kmajor_desc(k_stage + c * K_CHUNK_BYTES + k * 32);
-                        const uint32_t accumulate = (c | k) != 0 ? 1U : 0U;
-                        if (c < Q_TMEM_CHUNKS) {
-                            mma_ts(d, tmem_base + TMEM_Q + c * 32 + k * 8, k_desc, IDESC_QK, accumulate);
-                        } else {
-                            mma_ss(d, make_kmajor_desc(q_smem + (c - Q_TMEM_CHUNKS) * Q_CHUNK_BYTES + k * 32), k_desc, IDESC_QK,
-                                   accumulate);
-                        }
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t accumulate = (first && k == 0) ? 0U : 1U;
+                    if (shared) {
+                        mma_ss_split(s_tmem, q_lo + index * (Q_CHUNK_BYTES >> 4) + 2 * k, HI, k_lo + 2 * k, HI, IDESC_QK, accumulate);
+                    } else {
+                        mma_ts_split(s_tmem, tmem_base + TMEM_Q + index * 32 + k * 8, k_lo + 2 * k, HI, IDESC_QK, accumulate);
                     }
                 }
-                mma_commit(smem_u32(&bars->s_full[stage]));
-                mma_commit(smem_u32(&bars->empty_a[stage]));
             };
-            if (alive) {
-                issue_qk(0);
-            }
-            for (int j = 0; j < tile_count && alive; ++j) {
-                if (j + 1 < tile_count) {
-                    issue_qk(j + 1);
+            while (alive && next_segment(p, schedule, walker, seg, pair, pairs)) {
+                const int tile_count = seg.tile_end - seg.tile_begin;
+                const uint32_t seg_parity = segment_index & 1;
+                alive = mbar_wait(smem_u32(&bars->q_full), seg_parity, abort_flag, &absorbed_status) &&
+                        mbar_wait(smem_u32(&bars->q_tmem_ready), seg_parity, abort_flag, &absorbed_status);
+                for (int j = 0; j < tile_count && alive; ++j) {
+                    const int tile = tile_index + j;
+                    const int slot_a = tile % A_SLOTS;
+                    const int slot_b = tile % B_SLOTS;
+                    // ---- S = Q K^T: the five "A" chunks, then the four "B" chunks ----
+                    STAMP(1, tile, 0);
+                    alive = mbar_wait(smem_u32(&bars->full_a[slot_a]), (tile / A_SLOTS) & 1, abort_flag, &absorbed_status);
                     if (!alive) {
                         break;
                     }
-                }
-                const int stage = j & 1;
-                alive = mbar_wait(smem_u32(&bars->p_full[stage]), (j >> 1) & 1, abort_flag, &absorbed_status);
-                if (!alive) {
-                    break;
-                }
-                tc_fence_after_sync();
-                const uint32_t v_smem = stage_smem + stage * STAGE_BYTES + v_first * K_CHUNK_BYTES;
-                const uint32_t p_tmem = tmem_base + TMEM_S + stage * KEYS;
+                    STAMP(1, tile, 1);
+                    tc_fence_after_sync();
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    mma_ts(tmem_base + TMEM_O, p_tmem + k * 8, make_smem_desc(v_smem + k * 2048, K_CHUNK_BYTES, 1024), IDESC_PV,
-                           (j | k) != 0 ? 1U : 0U);
+                    for (int i = 0; i < A_CHUNKS; ++i) {
+                        const uint32_t k_lo = a_lo + (slot_a * A_CHUNKS + i) * CHUNK_LO;
+                        if (i < Q_SMEM_CHUNKS) {
+                            issue_slice(true, i, k_lo, i == 0);
+                        } else {
+                            issue_slice(false, a_ts_slot + i - Q_SMEM_CHUNKS, k_lo, false);
+                        }
+                    }
+                    mma_commit(smem_u32(&bars->empty_a[slot_a]));
+                    STAMP(1, tile, 2);
+                    alive = mbar_wait(smem_u32(&bars->full_b[slot_b]), (tile / B_SLOTS) & 1, abort_flag, &absorbed_status);
+                    if (!alive) {
+                        break;
+                    }
+                    STAMP(1, tile, 3);
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int i = 0; i < B_CHUNKS; ++i) {
+                        issue_slice(false, b_ts_slot + i, b_lo + (slot_b * B_CHUNKS + i) * CHUNK_LO, false);
+                    }
+                    mma_commit(smem_u32(&bars->s_full));
+                    STAMP(1, tile, 4);
+                    // ---- O (+)= P V ----
+                    alive = mbar_wait(smem_u32(&bars->p_full), tile & 1, abort_flag, &absorbed_status);
+                    if (!alive) {
+                        break;
+                    }
+                    STAMP(1, tile, 5);
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        mma_ts_split(tmem_base + TMEM_O, s_tmem + k * 8, v_lo + slot_b * B_CHUNKS * CHUNK_LO + k * (2048 >> 4), HI, IDESC_PV,
+                                     (j | k) != 0 ? 1U : 0U);
+                    }
+                    mma_commit(smem_u32(&bars->empty_b[slot_b]));
+                    STAMP(1, tile, 6);
                 }
-                mma_commit(smem_u32(&bars->empty_b[stage]));
-                mma_commit(smem_u32(&bars->o_done));
+                if (alive) {
+                    mma_commit(smem_u32(&bars->o_final));
+                }
+                tile_index += tile_count;
+                segment_index += 1;
             }
         }
     } else {
@@ -336,147 +535,165 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
         const int r = threadIdx.x;                       // row of the tile, 0..127
         const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
         const uint32_t o_tmem = tmem_base + lane_base + TMEM_O;
+        const uint32_t s_tmem = tmem_base + lane_base + TMEM_S;
         bool alive = true;
 
-        // ---- move Q columns 0..255 from the staging area to tensor memory ---
-        alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->q_stage_full), 0, abort_flag, &absorbed_status));
-        if (alive) {
-            const uint8_t* staging = smem_aligned + Q_SMEM_BYTES + STAGE_BYTES;
-#pragma unroll
-            for (int c = 0; c < Q_TMEM_CHUNKS; ++c) {
-                uint32_t values[32];
-                const uint8_t* row = staging + c * Q_CHUNK_BYTES + r * 128;
-#pragma unroll
-                for (int unit = 0; unit < 8; ++unit) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(row + ((unit ^ (r & 7)) * 16));
-                    values[unit * 4 + 0] = v.x;
-                    values[unit * 4 + 1] = v.y;
-                    values[unit * 4 + 2] = v.z;
-                    values[unit * 4 + 3] = v.w;
-                }
-                tmem_st_x32(tmem_base + lane_base + TMEM_Q + c * 32, values);
+        while (alive && next_segment(p, schedule, walker, seg, pair, pairs)) {
+            const int tile_count = seg.tile_end - seg.tile_begin;
+            const uint32_t seg_parity = segment_index & 1;
+            int valid_rows;      // rows of the tile that exist
+            int kv_end;          // keys >= kv_end are never visible in this segment
+            int min_limit;       // smallest per-row key limit; tiles past it need masking
+            int limit;           // this row sees keys < limit
+            if (decode) {
+                valid_rows = min(ROWS, p.heads - seg.row_tile * ROWS);
+                kv_end = min(p.lengths[seg.b], seg.tile_end * KEYS);
+                min_limit = kv_end;
+                limit = kv_end;
+            } else {
+                const int rows_total = p.sequence * p.heads;
+                const int first = seg.row_tile * ROWS;
+                valid_rows = min(ROWS, rows_total - first);
+                kv_end = (first + valid_rows - 1) / p.heads + 1;
+                min_limit = first / p.heads + 1;
+                limit = (first + min(r, valid_rows - 1)) / p.heads + 1;
             }
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(smem_u32(&bars->q_tmem_ready));
-        }
 
-        // per-row visibility limit: key index < limit
-        int limit;
-        if (p.mode == MODE_CAUSAL_PREFILL) {
-            limit = (row_tile * ROWS + min(r, valid_rows - 1)) / p.heads + 1;
-        } else {
-            limit = kv_end;
-        }
-        float m_ref = 0.0F;
-        float l_sum = 0.0F;
+            // ---- move the six staged Q chunks to tensor memory ---
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->q_stage_full), seg_parity, abort_flag, &absorbed_status));
+            if (!alive) {
+                break;
+            }
+            {
+#pragma unroll
+                for (int c = 0; c < Q_TMEM_CHUNKS; ++c) {
+                    uint32_t values[32];
+                    const uint8_t* row = b_ring_ptr + c * Q_CHUNK_BYTES + r * 128;
+#pragma unroll
+                    for (int unit = 0; unit < 8; ++unit) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(row + ((unit ^ (r & 7)) * 16));
+                        values[unit * 4 + 0] = v.x;
+                        values[unit * 4 + 1] = v.y;
+                        values[unit * 4 + 2] = v.z;
+                        values[unit * 4 + 3] = v.w;
+                    }
+                    tmem_st_x32(tmem_base + lane_base + TMEM_Q + c * 32, values);
+                }
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&bars->q_tmem_ready));
+            }
 
-        for (int j = 0; j < tile_count && alive; ++j) {
-            const int stage = j & 1;
-            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->s_full[stage]), (j >> 1) & 1, abort_flag, &absorbed_status));
+            float m_ref = 0.0F;
+            float l_sum = 0.0F;
+            for (int j = 0; j < tile_count && alive; ++j) {
+                const int tile = tile_index + j;
+                if (r == 0) STAMP(0, tile, 0);
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->s_full), tile & 1, abort_flag, &absorbed_status));
+                if (!alive) {
+                    break;
+                }
+                if (r == 0) STAMP(0, tile, 1);
+                tc_fence_after_sync();
+                uint32_t sb[KEYS];
+                tmem_ld_x32(s_tmem, sb);
+                tmem_ld_x32(s_tmem + 32, sb + 32);
+                tmem_wait_ld();
+                if (r == 0) STAMP(0, tile, 2);
+#ifdef DSCUDA_DEBUG_DUMP
+                if (p.debug != nullptr && j == 0 && segment_index == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+                    for (int n = 0; n < KEYS; ++n) {
+                        p.debug[r * KEYS + n] = __uint_as_float(sb[n]);
+                    }
+                }
+#endif
+                const int token0 = (seg.tile_begin + j) * KEYS;
+                if (token0 + KEYS > min_limit) {
+#pragma unroll
+                    for (int n = 0; n < KEYS; ++n) {
+                        sb[n] = token0 + n < limit ? sb[n] : 0xff800000U;
+                    }
+                }
+                if (token0 + KEYS > kv_end) {
+                    // Keys past the end may hold anything (the cache page is only
+                    // partly written); zero them so that 0 * V stays 0 in P V.
+                    uint8_t* v_rows = b_ring_ptr + (tile % B_SLOTS) * B_UNIT_BYTES;
+                    const int first_bad = kv_end - token0;               // 1..63
+                    const int bad_units = (KEYS - first_bad) * 8 * 4;    // 16-byte units in 4 chunks
+                    for (int u = r; u < bad_units; u += ROWS) {
+                        const int chunk = u / ((KEYS - first_bad) * 8);
+                        const int within = u % ((KEYS - first_bad) * 8);
+                        *reinterpret_cast<uint4*>(v_rows + chunk * K_CHUNK_BYTES + (first_bad + within / 8) * 128 + (within % 8) * 16) =
+                            make_uint4(0, 0, 0, 0);
+                    }
+                    fence_proxy_async_smem();
+                }
+                float mx0 = __uint_as_float(sb[0]), mx1 = __uint_as_float(sb[1]);
+#pragma unroll
+                for (int n = 2; n < KEYS; n += 2) {
+                    mx0 = fmaxf(mx0, __uint_as_float(sb[n]));
+                    mx1 = fmaxf(mx1, __uint_as_float(sb[n + 1]));
+                }
+                const float tile_max = fmaxf(mx0, mx1);
+                if (j == 0) {
+                    m_ref = tile_max;
+                } else {
+                    const bool grow = (tile_max - m_ref) * p.scale_log2 > RESCALE_THRESHOLD;
+                    if (__any_sync(0xffffffffU, grow)) {
+                        // S of this tile was issued after P V of the previous one, so its
+                        // completion implies that O is quiescent here.
+                        float alpha = 1.0F;
+                        if (grow) {
+                            alpha = exp2_approx((m_ref - tile_max) * p.scale_log2);
+                            m_ref = tile_max;
+                            l_sum *= alpha;
+                        }
+#pragma unroll
+                        for (int c = 0; c < HALF_V / 32; ++c) {
+                            uint32_t o[32];
+                            tmem_ld_x32(o_tmem + c * 32, o);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                            }
+                            tmem_st_x32(o_tmem + c * 32, o);
+                        }
+                    }
+                }
+                const float bias = -m_ref * p.scale_log2;
+                float sum0 = 0.0F, sum1 = 0.0F;
+#pragma unroll
+                for (int c = 0; c < KEYS / 32; ++c) {
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const float p0 = exp2_approx(fmaf(__uint_as_float(sb[c * 32 + 2 * e]), p.scale_log2, bias));
+                        const float p1 = exp2_approx(fmaf(__uint_as_float(sb[c * 32 + 2 * e + 1]), p.scale_log2, bias));
+                        sum0 += p0;
+                        sum1 += p1;
+                        packed[e] = pack_bf16x2(p0, p1);
+                    }
+                    tmem_st_x16(s_tmem + c * 16, packed);
+                }
+                l_sum += sum0 + sum1;
+                if (r == 0) STAMP(0, tile, 3);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&bars->p_full));
+                if (r == 0) STAMP(0, tile, 4);
+            }
+
+            if (alive) {
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->o_final), seg_parity, abort_flag, &absorbed_status));
+            }
             if (!alive) {
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t s_tmem = tmem_base + lane_base + TMEM_S + stage * KEYS;
-            uint32_t sb[KEYS];
-            tmem_ld_x32(s_tmem, sb);
-            tmem_ld_x32(s_tmem + 32, sb + 32);
-            tmem_wait_ld();
-#ifdef DSCUDA_DEBUG_DUMP
-            if (p.debug != nullptr && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-                for (int n = 0; n < KEYS; ++n) {
-                    p.debug[r * KEYS + n] = __uint_as_float(sb[n]);
-                }
-            }
-#endif
-            const int token0 = (tile_begin + j) * KEYS;
-            if (token0 + KEYS > min_limit) {
-#pragma unroll
-                for (int n = 0; n < KEYS; ++n) {
-                    sb[n] = token0 + n < limit ? sb[n] : 0xff800000U;
-                }
-            }
-            if (token0 + KEYS > kv_end) {
-                // Keys past the end may hold anything (the cache page is only
-                // partly written); zero them so that 0 * V stays 0 in P V.
-                uint8_t* v_rows = smem_aligned + Q_SMEM_BYTES + stage * STAGE_BYTES + v_first * K_CHUNK_BYTES;
-                const int first_bad = kv_end - token0;               // 1..63
-                const int bad_units = (KEYS - first_bad) * 8 * 4;    // 16-byte units in 4 chunks
-                for (int u = r; u < bad_units; u += ROWS) {
-                    const int chunk = u / ((KEYS - first_bad) * 8);
-                    const int within = u % ((KEYS - first_bad) * 8);
-                    *reinterpret_cast<uint4*>(v_rows + chunk * K_CHUNK_BYTES + (first_bad + within / 8) * 128 + (within % 8) * 16) =
-                        make_uint4(0, 0, 0, 0);
-                }
-                fence_proxy_async_smem();
-            }
-            float mx0 = __uint_as_float(sb[0]), mx1 = __uint_as_float(sb[1]);
-#pragma unroll
-            for (int n = 2; n < KEYS; n += 2) {
-                mx0 = fmaxf(mx0, __uint_as_float(sb[n]));
-                mx1 = fmaxf(mx1, __uint_as_float(sb[n + 1]));
-            }
-            const float tile_max = fmaxf(mx0, mx1);
-            if (j == 0) {
-                m_ref = tile_max;
-            } else {
-                const bool grow = (tile_max - m_ref) * p.scale_log2 > RESCALE_THRESHOLD;
-                if (__any_sync(0xffffffffU, grow)) {
-                    // O must be quiescent: wait for P V of the previous tile.
-                    alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->o_done), (j - 1) & 1, abort_flag, &absorbed_status));
-                    if (!alive) {
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    float alpha = 1.0F;
-                    if (grow) {
-                        alpha = exp2_approx((m_ref - tile_max) * p.scale_log2);
-                        m_ref = tile_max;
-                        l_sum *= alpha;
-                    }
-#pragma unroll
-                    for (int c = 0; c < HALF_V / 32; ++c) {
-                        uint32_t o[32];
-                        tmem_ld_x32(o_tmem + c * 32, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-                        }
-                        tmem_st_x32(o_tmem + c * 32, o);
-                    }
-                }
-            }
-            const float bias = -m_ref * p.scale_log2;
-            float sum0 = 0.0F, sum1 = 0.0F;
-#pragma unroll
-            for (int c = 0; c < KEYS / 32; ++c) {
-                uint32_t packed[16];
-#pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const float p0 = exp2_approx(fmaf(__uint_as_float(sb[c * 32 + 2 * e]), p.scale_log2, bias));
-                    const float p1 = exp2_approx(fmaf(__uint_as_float(sb[c * 32 + 2 * e + 1]), p.scale_log2, bias));
-                    sum0 += p0;
-                    sum1 += p1;
-                    packed[e] = pack_bf16x2(p0, p1);
-                }
-                tmem_st_x16(s_tmem + c * 16, packed);
-            }
-            l_sum += sum0 + sum1;
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(smem_u32(&bars->p_full[stage]));
-        }
-
-        if (alive) {
-            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->o_done), (tile_count - 1) & 1, abort_flag, &absorbed_status));
-        }
-        if (alive) {
-            tc_fence_after_sync();
             const bool valid = r < valid_rows;
 #ifdef DSCUDA_DEBUG_DUMP
-            if (p.debug != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+            if (p.debug != nullptr && segment_index == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
                 float* dump = p.debug + ROWS * KEYS + r * 258;
                 for (int c = 0; c < HALF_V / 32; ++c) {
                     uint32_t o[32];
@@ -490,10 +707,10 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                 dump[257] = m_ref;
             }
 #endif
-            if (p.mode == MODE_CAUSAL_PREFILL) {
-                const int row = row_tile * ROWS + r;                 // (token, head) index inside the sequence
+            if (!decode) {
+                const int row = seg.row_tile * ROWS + r;                 // (token, head) index inside the sequence
                 const float inverse = 1.0F / l_sum;
-                __nv_bfloat16* out_row = p.out + (static_cast<size_t>(b) * p.sequence * p.heads + row) * RANK + half * HALF_V;
+                __nv_bfloat16* out_row = p.out + (static_cast<size_t>(seg.b) * p.sequence * p.heads + row) * RANK + half * HALF_V;
 #pragma unroll
                 for (int c = 0; c < HALF_V / 32; ++c) {
                     uint32_t o[32];
@@ -514,14 +731,22 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                 if (valid && half == 0) {
                     const int token = row / p.heads;
                     const int head = row % p.heads;
-                    p.lse[(static_cast<size_t>(b) * p.heads + head) * p.sequence + token] = m_ref * p.scale + logf(l_sum);
+                    p.lse[(static_cast<size_t>(seg.b) * p.heads + head) * p.sequence + token] = m_ref * p.scale + logf(l_sum);
                 }
             } else {
-                const int head = row_tile * ROWS + r;
-                float* record = p.workspace + ((static_cast<size_t>(b) * p.heads + (valid ? head : 0)) * p.splits + split) * (RANK + 2);
+                const int head = seg.row_tile * ROWS + (valid ? r : 0);
+                float* records = p.workspace + (static_cast<size_t>(seg.b) * p.heads + head) * p.splits * (RANK + 2);
+                float* record = records + static_cast<size_t>(seg.slot) * (RANK + 2);
                 if (valid && half == 0) {
                     record[0] = m_ref * p.scale;
                     record[1] = l_sum;
+                    if (seg.last_of_unit) {
+                        // partial slots this sequence does not use carry no weight
+                        for (int s = seg.slot + 1; s < p.splits; ++s) {
+                            records[static_cast<size_t>(s) * (RANK + 2)] = -INFINITY;
+                            records[static_cast<size_t>(s) * (RANK + 2) + 1] = 0.0F;
+                        }
+                    }
                 }
 #pragma unroll
                 for (int c = 0; c < HALF_V / 32; ++c) {
@@ -537,6 +762,11 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                     }
                 }
             }
+            // the accumulator and the Q columns in tensor memory may be overwritten by
+            // the next segment only after every row has been read out
+            tc_fence_before_sync();
+            tile_index += tile_count;
+            segment_index += 1;
         }
     }
 
@@ -608,6 +838,21 @@ void configure_kernel() {
     }
 }
 
+int multiprocessor_count() {
+    static int cached[64] = {};
+    int device = 0;
+    CUDA_CHECK(cudaGetDevice(&device));
+    if (device >= 0 && device < 64 && cached[device] > 0) {
+        return cached[device];
+    }
+    int count = 0;
+    CUDA_CHECK(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device));
+    if (device >= 0 && device < 64) {
+        cached[device] = count;
+    }
+    return count;
+}
+
 void check_absorbed_shape(int kv_rank, int rope_size) {
     // kernels/attention/mla/sm89.cu:20-24 of the reference: same condition, same message.
     if (kv_rank != MLA_KV_RANK || rope_size != MLA_ROPE_SIZE) {
@@ -632,6 +877,7 @@ namespace internal {
 
 #ifdef DSCUDA_DEBUG_DUMP
 float* absorbed_debug_buffer = nullptr;
+long long* absorbed_debug_stamps = nullptr;
 #endif
 
 int absorbed_device_status(bool reset) {
@@ -682,6 +928,7 @@ void mla_compressed_attention_forward_cuda(__nv_bfloat16* output, float* logsume
     params.scale_log2 = scale * 1.4426950408889634F;
 #ifdef DSCUDA_DEBUG_DUMP
     params.debug = internal::absorbed_debug_buffer;
+    params.stamps = internal::absorbed_debug_stamps;
 #endif
     configure_kernel();
     const dim3 grid(1, static_cast<unsigned>((rows_per_sequence + ROWS - 1) / ROWS * 2), batch_size);
@@ -738,9 +985,12 @@ void mla_decode_forward_cuda(__nv_bfloat16* output, float* logsumexp, const __nv
     params.scale_log2 = scale * 1.4426950408889634F;
 #ifdef DSCUDA_DEBUG_DUMP
     params.debug = internal::absorbed_debug_buffer;
+    params.stamps = internal::absorbed_debug_stamps;
 #endif
     configure_kernel();
-    const dim3 grid(splits, static_cast<unsigned>((heads + ROWS - 1) / ROWS * 2), batch_size);
+    // one CTA per SM, in pairs that share a key range (the two halves of the value columns)
+    const int pairs = std::max(1, multiprocessor_count() / 2);
+    const dim3 grid(2 * pairs, 1, 1);
     absorbed_attention_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(params);
     CUDA_CHECK(cudaGetLastError());
     decode_combine_kernel<<<dim3(heads, batch_size), 128, 0, stream>>>(output, logsumexp, workspace, heads, splits);

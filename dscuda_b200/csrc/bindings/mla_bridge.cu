@@ -113,7 +113,11 @@ extern "C" int dscuda_mla_device_status(int reset) {
 #ifdef DSCUDA_DEBUG_DUMP
 // Diagnostic builds only: raw score / accumulator dumps of the first CTA.
 #include "../attention/attention_internal.h"
-namespace dscuda { namespace internal { extern float* absorbed_debug_buffer; } }
+namespace dscuda { namespace internal { extern float* absorbed_debug_buffer; extern long long* absorbed_debug_stamps; } }
+
+extern "C" void dscuda_debug_set_absorbed_stamps(long long* stamps) {
+    dscuda::internal::absorbed_debug_stamps = stamps;
+}
 
 extern "C" int dscuda_debug_prefill_forward(bf16* output, float* lse, const bf16* q_nope, const bf16* q_pe, const bf16* k_nope,
                                             const bf16* k_pe, const bf16* v, const int* cu_seqlens, int batch, int max_sequence,
