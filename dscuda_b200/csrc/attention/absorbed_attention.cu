@@ -47,7 +47,7 @@ constexpr int ROPE = MLA_ROPE_SIZE;             // 64
 constexpr int WIDTH = RANK + ROPE;              // 576
 constexpr int CHUNKS = WIDTH / 64;              // 9 column chunks of 64
 constexpr int HALF_V = RANK / 2;                // value columns per CTA
-constexpr int Q_TMEM_CHUNKS = 6;                // Q columns 0..383 live in tensor memory
+constexpr int Q_TMEM_CHUNKS = 4;                // the Q chunks that face this CTA's V chunks live in tensor memory
 constexpr int Q_SMEM_CHUNKS = CHUNKS - Q_TMEM_CHUNKS;
 constexpr int Q_CHUNK_BYTES = ROWS * 128;       // 16 KB
 constexpr int K_CHUNK_BYTES = KEYS * 128;       // 8 KB
@@ -56,10 +56,10 @@ constexpr int B_CHUNKS = 4;                     // key chunks of a tile that are
 constexpr int A_UNIT_BYTES = A_CHUNKS * K_CHUNK_BYTES;       // 40 KB
 constexpr int B_UNIT_BYTES = B_CHUNKS * K_CHUNK_BYTES;       // 32 KB
 constexpr int A_SLOTS = 2;
-constexpr int B_SLOTS = 3;
-constexpr int Q_SMEM_BYTES = Q_SMEM_CHUNKS * Q_CHUNK_BYTES;  // 48 KB
+constexpr int B_SLOTS = 2;
+constexpr int Q_SMEM_BYTES = Q_SMEM_CHUNKS * Q_CHUNK_BYTES;  // 80 KB
 constexpr int A_RING_BYTES = A_SLOTS * A_UNIT_BYTES;         // 80 KB
-constexpr int B_RING_BYTES = B_SLOTS * B_UNIT_BYTES;         // 96 KB
+constexpr int B_RING_BYTES = B_SLOTS * B_UNIT_BYTES;         // 64 KB
 constexpr int MISC_BYTES = 1024;
 constexpr int SMEM_BYTES = Q_SMEM_BYTES + A_RING_BYTES + B_RING_BYTES + MISC_BYTES + 1024;
 constexpr int THREADS = 192;
@@ -67,8 +67,8 @@ constexpr int MMA_WARP = 4;
 constexpr int LOAD_WARP = 5;
 constexpr int TMEM_COLUMNS = 512;
 constexpr int TMEM_O = 0;                       // 256 columns
-constexpr int TMEM_S = 256;                     // 64 columns
-constexpr int TMEM_Q = 320;                     // 192 columns = 6 chunks x 32
+constexpr int TMEM_S = 256;                     // 2 x 64 columns
+constexpr int TMEM_Q = 384;                     // 128 columns = 4 chunks x 32
 constexpr float RESCALE_THRESHOLD = 8.0F;
 static_assert(Q_TMEM_CHUNKS * Q_CHUNK_BYTES <= B_RING_BYTES, "Q staging must fit in the value ring");
 static_assert(SMEM_BYTES <= 232448, "shared memory budget");
@@ -136,8 +136,8 @@ struct AbsorbedBarriers {
     uint64_t empty_a[A_SLOTS];
     uint64_t full_b[B_SLOTS];   // ring of the four chunks that are also this CTA's V
     uint64_t empty_b[B_SLOTS];
-    uint64_t s_full;            // one phase per tile
-    uint64_t p_full;            // one phase per tile
+    uint64_t s_full[2];         // per S buffer
+    uint64_t p_full[2];         // per S buffer
     uint64_t o_final;           // one phase per segment: the last P V has finished
     uint32_t tmem_base;
     int abort_flag;
@@ -268,8 +268,10 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
             mbar_init(smem_u32(&bars->full_b[i]), 1);
             mbar_init(smem_u32(&bars->empty_b[i]), 1);
         }
-        mbar_init(smem_u32(&bars->s_full), 1);
-        mbar_init(smem_u32(&bars->p_full), ROWS);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&bars->s_full[i]), 1);
+            mbar_init(smem_u32(&bars->p_full[i]), ROWS);
+        }
         mbar_init(smem_u32(&bars->o_final), 1);
         bars->abort_flag = 0;
         mbar_init_fence();
@@ -323,24 +325,13 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
     const Schedule schedule = bars->schedule;
 
     // Key chunk c holds columns 64c..64c+63 (c = 8: the rotary columns).  Chunks
-    // v_first..v_first+3 are this CTA's V ("B" group); the other five are the "A" group.
-    // Six Q chunks sit in tensor memory (the B group's four and two of the A group),
-    // three in shared memory.  Inside a tile the three shared-memory slices are issued
-    // first and the six tensor-memory slices after them: an A-from-shared-memory MMA
-    // that follows A-from-tensor-memory MMAs on the same accumulator costs about three
-    // times its normal issue time, the other order costs nothing.
+    // v_first..v_first+3 are this CTA's V (the "B" group); the matching four Q chunks
+    // sit in tensor memory.  The other five key chunks are the "A" group; their Q
+    // chunks stay in shared memory.  A tile's S is accumulated A group first
+    // (Q from shared memory), B group second (Q from tensor memory): the opposite
+    // order on one accumulator costs about three times the issue time.
     const int v_first = half * 4;
-    //   A-group order: half 0 -> 6,7,8,4,5   half 1 -> 2,3,8,0,1   (first three: Q in shared memory)
-    auto a_chunk = [&](int i) -> int {
-        const int table0[A_CHUNKS] = {6, 7, 8, 4, 5};
-        const int table1[A_CHUNKS] = {2, 3, 8, 0, 1};
-        return half == 0 ? table0[i] : table1[i];
-    };
-    // tensor-memory slot t (0..5) holds Q chunk: half 0 -> t, half 1 -> 0,1,4,5,6,7
-    auto tmem_chunk = [&](int t) -> int { return half == 0 ? t : (t < 2 ? t : t + 2); };
-    // slots of the A group's two tensor-memory slices and of the B group's four
-    const int a_ts_slot = half == 0 ? 4 : 0;
-    const int b_ts_slot = half == 0 ? 0 : 2;
+    auto a_chunk = [&](int i) -> int { return half == 0 ? 4 + i : (i < 4 ? i : 8); };
 
     Walker walker;
     walker.unit = (decode && p.splits == 1) ? pair : schedule.first_unit;
@@ -382,7 +373,7 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                     const uint32_t stage_bar = smem_u32(&bars->q_stage_full);
                     mbar_arrive_expect_tx(stage_bar, Q_TMEM_CHUNKS * Q_CHUNK_BYTES);
                     for (int c = 0; c < Q_TMEM_CHUNKS; ++c) {
-                        tma_load_2d(b_ring + c * Q_CHUNK_BYTES, &p.q_lat, stage_bar, tmem_chunk(c) * 64, q_row0);
+                        tma_load_2d(b_ring + c * Q_CHUNK_BYTES, &p.q_lat, stage_bar, (v_first + c) * 64, q_row0);
                     }
                 }
             }
@@ -453,75 +444,86 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
             const uint32_t a_lo = smem_desc_lo(a_ring, 16);
             const uint32_t b_lo = smem_desc_lo(b_ring, 16);
             const uint32_t v_lo = smem_desc_lo(b_ring, K_CHUNK_BYTES);
-            const uint32_t s_tmem = tmem_base + TMEM_S;
             bool alive = true;
-            // one 64-column slice of the 576-deep contraction against the key chunk at k_lo:
-            // Q from shared-memory chunk `index` (shared == true) or tensor-memory slot `index`
-            auto issue_slice = [&](bool shared, int index, uint32_t k_lo, bool first) {
+            // A group of tile `tile`: five slices with Q from shared memory, starts the accumulator
+            auto issue_a_part = [&](int tile) {
+                const int slot_a = tile % A_SLOTS;
+                alive = mbar_wait(smem_u32(&bars->full_a[slot_a]), (tile / A_SLOTS) & 1, abort_flag, &absorbed_status);
+                if (!alive) {
+                    return;
+                }
+                tc_fence_after_sync();
+                const uint32_t s_tmem = tmem_base + TMEM_S + (tile & 1) * KEYS;
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint32_t accumulate = (first && k == 0) ? 0U : 1U;
-                    if (shared) {
-                        mma_ss_split(s_tmem, q_lo + index * (Q_CHUNK_BYTES >> 4) + 2 * k, HI, k_lo + 2 * k, HI, IDESC_QK, accumulate);
-                    } else {
-                        mma_ts_split(s_tmem, tmem_base + TMEM_Q + index * 32 + k * 8, k_lo + 2 * k, HI, IDESC_QK, accumulate);
+                for (int i = 0; i < A_CHUNKS; ++i) {
+                    const uint32_t k_lo = a_lo + (slot_a * A_CHUNKS + i) * CHUNK_LO;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        mma_ss_split(s_tmem, q_lo + i * (Q_CHUNK_BYTES >> 4) + 2 * k, HI, k_lo + 2 * k, HI, IDESC_QK, (i | k) != 0 ? 1U : 0U);
                     }
                 }
+                mma_commit(smem_u32(&bars->empty_a[slot_a]));
+            };
+            // B group of tile `tile`: four slices with Q from tensor memory, completes S
+            auto issue_b_part = [&](int tile) {
+                const int slot_b = tile % B_SLOTS;
+                alive = mbar_wait(smem_u32(&bars->full_b[slot_b]), (tile / B_SLOTS) & 1, abort_flag, &absorbed_status);
+                if (!alive) {
+                    return;
+                }
+                tc_fence_after_sync();
+                const uint32_t s_tmem = tmem_base + TMEM_S + (tile & 1) * KEYS;
+#pragma unroll
+                for (int i = 0; i < B_CHUNKS; ++i) {
+                    const uint32_t k_lo = b_lo + (slot_b * B_CHUNKS + i) * CHUNK_LO;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        mma_ts_split(s_tmem, tmem_base + TMEM_Q + i * 32 + k * 8, k_lo + 2 * k, HI, IDESC_QK, 1U);
+                    }
+                }
+                mma_commit(smem_u32(&bars->s_full[tile & 1]));
             };
             while (alive && next_segment(p, schedule, walker, seg, pair, pairs)) {
                 const int tile_count = seg.tile_end - seg.tile_begin;
                 const uint32_t seg_parity = segment_index & 1;
                 alive = mbar_wait(smem_u32(&bars->q_full), seg_parity, abort_flag, &absorbed_status) &&
                         mbar_wait(smem_u32(&bars->q_tmem_ready), seg_parity, abort_flag, &absorbed_status);
+                if (alive) {
+                    tc_fence_after_sync();
+                    issue_a_part(tile_index);
+                }
+                if (alive) {
+                    issue_b_part(tile_index);
+                }
                 for (int j = 0; j < tile_count && alive; ++j) {
                     const int tile = tile_index + j;
-                    const int slot_a = tile % A_SLOTS;
                     const int slot_b = tile % B_SLOTS;
-                    // ---- S = Q K^T: the five "A" chunks, then the four "B" chunks ----
-                    STAMP(1, tile, 0);
-                    alive = mbar_wait(smem_u32(&bars->full_a[slot_a]), (tile / A_SLOTS) & 1, abort_flag, &absorbed_status);
-                    if (!alive) {
-                        break;
-                    }
-                    STAMP(1, tile, 1);
-                    tc_fence_after_sync();
-#pragma unroll
-                    for (int i = 0; i < A_CHUNKS; ++i) {
-                        const uint32_t k_lo = a_lo + (slot_a * A_CHUNKS + i) * CHUNK_LO;
-                        if (i < Q_SMEM_CHUNKS) {
-                            issue_slice(true, i, k_lo, i == 0);
-                        } else {
-                            issue_slice(false, a_ts_slot + i - Q_SMEM_CHUNKS, k_lo, false);
+                    // the next tile's A group runs on the tensor core while this tile's softmax is computed
+                    if (j + 1 < tile_count) {
+                        issue_a_part(tile + 1);
+                        if (!alive) {
+                            break;
                         }
                     }
-                    mma_commit(smem_u32(&bars->empty_a[slot_a]));
-                    STAMP(1, tile, 2);
-                    alive = mbar_wait(smem_u32(&bars->full_b[slot_b]), (tile / B_SLOTS) & 1, abort_flag, &absorbed_status);
-                    if (!alive) {
-                        break;
-                    }
-                    STAMP(1, tile, 3);
-                    tc_fence_after_sync();
-#pragma unroll
-                    for (int i = 0; i < B_CHUNKS; ++i) {
-                        issue_slice(false, b_ts_slot + i, b_lo + (slot_b * B_CHUNKS + i) * CHUNK_LO, false);
-                    }
-                    mma_commit(smem_u32(&bars->s_full));
                     STAMP(1, tile, 4);
                     // ---- O (+)= P V ----
-                    alive = mbar_wait(smem_u32(&bars->p_full), tile & 1, abort_flag, &absorbed_status);
+                    alive = mbar_wait(smem_u32(&bars->p_full[tile & 1]), (tile >> 1) & 1, abort_flag, &absorbed_status);
                     if (!alive) {
                         break;
                     }
                     STAMP(1, tile, 5);
                     tc_fence_after_sync();
+                    const uint32_t p_tmem = tmem_base + TMEM_S + (tile & 1) * KEYS;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        mma_ts_split(tmem_base + TMEM_O, s_tmem + k * 8, v_lo + slot_b * B_CHUNKS * CHUNK_LO + k * (2048 >> 4), HI, IDESC_PV,
+                        mma_ts_split(tmem_base + TMEM_O, p_tmem + k * 8, v_lo + slot_b * B_CHUNKS * CHUNK_LO + k * (2048 >> 4), HI, IDESC_PV,
                                      (j | k) != 0 ? 1U : 0U);
                     }
                     mma_commit(smem_u32(&bars->empty_b[slot_b]));
                     STAMP(1, tile, 6);
+                    if (j + 1 < tile_count) {
+                        issue_b_part(tile + 1);
+                    }
                 }
                 if (alive) {
                     mma_commit(smem_u32(&bars->o_final));
@@ -535,7 +537,6 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
         const int r = threadIdx.x;                       // row of the tile, 0..127
         const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
         const uint32_t o_tmem = tmem_base + lane_base + TMEM_O;
-        const uint32_t s_tmem = tmem_base + lane_base + TMEM_S;
         bool alive = true;
 
         while (alive && next_segment(p, schedule, walker, seg, pair, pairs)) {
@@ -559,7 +560,7 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                 limit = (first + min(r, valid_rows - 1)) / p.heads + 1;
             }
 
-            // ---- move the six staged Q chunks to tensor memory ---
+            // ---- move the four staged Q chunks to tensor memory ---
             alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->q_stage_full), seg_parity, abort_flag, &absorbed_status));
             if (!alive) {
                 break;
@@ -588,8 +589,9 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
             float l_sum = 0.0F;
             for (int j = 0; j < tile_count && alive; ++j) {
                 const int tile = tile_index + j;
+                const uint32_t s_tmem = tmem_base + lane_base + TMEM_S + (tile & 1) * KEYS;
                 if (r == 0) STAMP(0, tile, 0);
-                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->s_full), tile & 1, abort_flag, &absorbed_status));
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->s_full[tile & 1]), (tile >> 1) & 1, abort_flag, &absorbed_status));
                 if (!alive) {
                     break;
                 }
@@ -680,7 +682,7 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                 if (r == 0) STAMP(0, tile, 3);
                 tmem_wait_st();
                 tc_fence_before_sync();
-                mbar_arrive(smem_u32(&bars->p_full));
+                mbar_arrive(smem_u32(&bars->p_full[tile & 1]));
                 if (r == 0) STAMP(0, tile, 4);
             }
 
