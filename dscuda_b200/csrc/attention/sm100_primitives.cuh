@@ -67,11 +67,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 
+// Non-blocking probe of the same condition.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
 // Waits for the phase with the given parity to complete.  Gives up when the
 // time limit passes or when another thread of the CTA has already given up
 // (`abort_flag`, in shared memory); then it raises both flags and returns
 // false, and the caller must leave its loop and go to the common teardown.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word) {
+    if (mbar_test_wait(bar, parity)) {
+        return true;
+    }
     if (mbar_try_wait(bar, parity)) {
         return true;
     }
