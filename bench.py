@@ -224,6 +224,7 @@ def run_ours(args, rank, world, device):
 
     decode = bench_decode(mla, oracle, device, peaks) if world == 1 and not args.skip_decode else None
     cpu = cpu_baseline(oracle, 12.0) if world == 1 and not args.skip_cpu else None
+    varlen = bench_varlen(mla, oracle, device, peaks) if world == 1 and not args.skip_decode else None
 
     if rank != 0:
         return None
@@ -246,7 +247,7 @@ def run_ours(args, rank, world, device):
                      "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": achieved / peaks["tensor"],
                      "peak_source": peaks["source"] + " sustained cuBLAS bf16", "frac_of_burst_peak": achieved / peaks["tensor_burst"],
                      "traffic": None},
-        "cpu_baseline": cpu, "decode": decode,
+        "cpu_baseline": cpu, "decode": decode, "varlen": varlen,
     }
     return line
 
@@ -271,6 +272,35 @@ def bench_decode(mla, oracle, device, peaks, steps=20, warmup=3, splits=16, batc
             "tokens": total_tokens, "algorithmic_bytes": algorithmic, "splits": splits, "tflops": flops / seconds / 1e12,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"],
                          "peak_source": peaks["source"] + " copy bandwidth", "tensor_frac": flops / seconds / 1e12 / peaks["tensor_burst"]}}
+
+
+def bench_varlen(mla, oracle, device, peaks, heads=16, steps=3, warmup=1):
+    """Packed long-context forward+backward: the 16 sequence lengths of seed 4 (log-uniform in
+    [512, 32768], 121 320 tokens), 16 heads per GPU (the per-GPU shard of the 128-head job)."""
+    lengths = oracle.varlen_lengths()
+    total = sum(lengths)
+    g = torch.Generator(device=device).manual_seed(4)
+
+    def draw(*shape, std=1.0):
+        return (torch.randn(*shape, device=device, generator=g, dtype=torch.float32) * std).bfloat16()
+
+    x = (draw(total, heads, 128), draw(total, heads, 64), draw(total, heads, 128), draw(total, 1, 64), draw(total, heads, 128))
+    dout = draw(total, heads, 128, std=0.1)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=device)
+    out = torch.empty_like(x[4])
+    lse = torch.empty(heads, total, device=device)
+    workspace = mla.prefill_backward_workspace(len(lengths), max(lengths), total, heads, device)
+    grads = (torch.empty(total, heads, 192, device=device, dtype=torch.bfloat16), torch.empty_like(x[2]), torch.empty_like(x[3]), torch.empty_like(x[4]))
+
+    def step():
+        mla.prefill_forward(*x, SCALE, cu, max(lengths), output=out, lse=lse)
+        mla.prefill_backward(dout, out, lse, *x, SCALE, cu, max(lengths), workspace=workspace, grads=grads)
+
+    seconds = time_steps(step, steps, warmup, lambda: None) / steps
+    flops = sum(causal_pairs(n) for n in lengths) * heads * (FWD_FLOP_PER_PAIR + BWD_FLOP_PER_PAIR)
+    tflops = flops / seconds / 1e12
+    return {"metric": "packed long-context MLA fwd+bwd TFLOP/s per GPU", "value": tflops, "unit": "TFLOP/s", "ms_per_step": seconds * 1e3,
+            "tokens": total, "sequences": len(lengths), "heads_per_gpu": heads, "frac_of_measured_sustained_peak": tflops / peaks["tensor"]}
 
 
 def cpu_baseline(oracle, budget_seconds):
@@ -332,7 +362,7 @@ def run_reference(args, rank, world):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=10)
+    parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--workload", default="train", choices=tuple(WORKLOADS))

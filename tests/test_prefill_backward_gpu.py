@@ -119,3 +119,49 @@ def test_linearity_in_dout_at_training_size(gpu):
     ref = oracle.prefill_backward(dout[:, :2048, :1].cpu().contiguous(), out[:, :2048, :1].cpu().contiguous(),
                                   lse[:, :1, :2048].cpu().contiguous(), *tensors, SCALE)
     assert rel_l2(g1[0][:, :2048, :1].float().cpu(), ref[0]) <= 1e-2
+
+
+def test_long_context_packed_lengths(gpu):
+    """The 16 packed sequence lengths of the long-context configuration (log-uniform
+    in [512, 32768], seed 4; 121 320 tokens) on 2 heads: finite outputs, each short
+    sequence checked against the oracle, and the dk_pe head-sum equal to the sum of
+    two single-head runs (what a head-sharded multi-GPU run adds up)."""
+    from dscuda_b200 import mla
+    lengths = oracle.varlen_lengths()
+    total = sum(lengths)
+    heads = 2
+    generator = torch.Generator(device=gpu).manual_seed(4)
+
+    def draw(*shape, std=1.0):
+        return (torch.randn(*shape, device=gpu, generator=generator, dtype=torch.float32) * std).bfloat16()
+
+    q_nope, q_pe, k_nope, k_pe, v = draw(total, heads, 128), draw(total, heads, 64), draw(total, heads, 128), draw(total, 1, 64), draw(total, heads, 128)
+    dout = draw(total, heads, 128, std=0.1)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=gpu)
+    out, lse = mla.prefill_forward(q_nope, q_pe, k_nope, k_pe, v, SCALE, cu, max(lengths))
+    grads = mla.prefill_backward(dout, out, lse, q_nope, q_pe, k_nope, k_pe, v, SCALE, cu, max(lengths))
+    torch.cuda.synchronize()
+    assert mla.device_status() == 0
+    for tensor in (out, lse, *grads):
+        assert bool(torch.isfinite(tensor.float()).all())
+    # the three shortest sequences against the oracle (each is an independent causal problem)
+    starts = [0] + list(torch.tensor(lengths).cumsum(0))
+    for index in sorted(range(len(lengths)), key=lambda i: lengths[i])[:3]:
+        a, b = int(starts[index]), int(starts[index + 1])
+        cpu = [t[a:b][None].cpu().contiguous() for t in (q_nope, q_pe, k_nope, k_pe, v)]
+        ref_out, ref_lse = oracle.prefill_forward(*cpu, SCALE)
+        assert float((out[a:b].float().cpu() - ref_out[0]).abs().max()) <= 1e-2 * float(ref_out.abs().max())
+        assert float((lse[:, a:b].cpu() - ref_lse[0]).abs().max()) <= 1e-3
+        reference = oracle.prefill_backward(dout[a:b][None].cpu(), out[a:b][None].cpu(), lse[:, a:b][None].cpu(), *cpu, SCALE)
+        check_grads([g[a:b][None].cpu() for g in grads], reference)
+    # head sharding: one head at a time gives the same per-head gradients and dk_pe partial sums that add up
+    partial_sum = torch.zeros(total, 64, device=gpu)
+    for h in range(heads):
+        sl = [t[:, h:h + 1].contiguous() for t in (q_nope, q_pe, k_nope)] + [k_pe, v[:, h:h + 1].contiguous()]
+        o1, l1 = mla.prefill_forward(*sl, SCALE, cu, max(lengths))
+        workspace = mla.prefill_backward_workspace(len(lengths), max(lengths), total, 1, gpu)
+        g1 = mla.prefill_backward(dout[:, h:h + 1].contiguous(), o1, l1, *sl, SCALE, cu, max(lengths), workspace=workspace)
+        torch.cuda.synchronize()
+        assert torch.equal(o1, out[:, h:h + 1]) and torch.equal(g1[0], grads[0][:, h:h + 1]) and torch.equal(g1[3], grads[3][:, h:h + 1])
+        partial_sum += workspace[: total * 64 * 4].view(torch.float32).reshape(total, 64)
+    assert rel_l2(partial_sum.cpu(), grads[2].float().reshape(total, 64).cpu()) <= 5e-3
