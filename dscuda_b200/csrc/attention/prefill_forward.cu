@@ -37,7 +37,7 @@ constexpr int HEAD_V = 128;                 // value width
 constexpr int CHUNK_BYTES = 16384;          // [128 rows x 64 bf16] or [64 keys x 128 bf16]
 constexpr int V_CHUNKS = TILE_N / 64;       // V tile = 2 chunks of 64 keys
 constexpr int SOFTMAX_THREADS = 256;
-constexpr int FORWARD_THREADS = 320;
+constexpr int FORWARD_THREADS = 384;     // warps 10 and 11 only complete the third warpgroup for setmaxnreg
 constexpr int MMA_WARP = 8;
 constexpr int LOAD_WARP = 9;
 constexpr int TMEM_COLUMNS = 512;           // S0 | S1 | O0 | O1, 128 columns each
@@ -180,163 +180,182 @@ __global__ void __launch_bounds__(FORWARD_THREADS, 1) attention_forward_kernel(c
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
 
-    if (warp == LOAD_WARP) {
-        // =================== TMA producer ===================================
-        if (lane == 0) {
-            auto load_q = [&](int i) {
-                const uint32_t bar = smem_u32(&bars->q_full[i]);
-                mbar_arrive_expect_tx(bar, KQ * CHUNK_BYTES);
-                const int y = row0 + q_start + i * TILE_M;
-                for (int c = 0; c < KQ; ++c) {
-                    const uint32_t dst = q_smem + (i * KQ + c) * CHUNK_BYTES;
-                    if (KQ == 3 && c == 2) {
-                        tma_load_2d(dst, &p.q_pe, bar, head * 64, y);
-                    } else {
-                        tma_load_2d(dst, &p.q_main, bar, head * 128 + c * 64, y);
-                    }
-                }
-            };
-            bool alive = true;
-            int chunk = 0;
-            // Returns the destination of ring chunk `chunk` once it is free, 0 on abort.
-            auto acquire = [&](uint32_t& bar) -> uint32_t {
-                const int slot = chunk % L::RING;
-                const int use = chunk / L::RING;
-                if (use > 0 && !mbar_wait(smem_u32(&bars->ring_empty[slot]), (use - 1) & 1, abort_flag, &forward_status)) {
-                    alive = false;
-                    return 0;
-                }
-                bar = smem_u32(&bars->ring_full[slot]);
-                mbar_arrive_expect_tx(bar, CHUNK_BYTES);
-                ++chunk;
-                return ring_smem + slot * CHUNK_BYTES;
-            };
-            load_q(0);
-            for (int j = 0; j < tile_count && alive; ++j) {
-                const int y = row0 + j * TILE_N;
-                for (int c = 0; c < KQ && alive; ++c) {
-                    uint32_t bar;
-                    const uint32_t dst = acquire(bar);
-                    if (dst == 0) {
-                        break;
-                    }
-                    if (KQ == 3 && c == 2) {
-                        tma_load_2d(dst, &p.k_pe, bar, 0, y);
-                    } else {
-                        tma_load_2d(dst, &p.k_main, bar, kv_head * 128 + c * 64, y);
-                    }
-                }
-                if (j == 0 && tiles[1] > 0) {
-                    load_q(1);
-                }
-                for (int half = 0; half < V_CHUNKS && alive; ++half) {
-                    uint32_t bar;
-                    const uint32_t dst = acquire(bar);
-                    if (dst == 0) {
-                        break;
-                    }
-                    tma_load_2d(dst, &p.v, bar, kv_head * 128, y + half * 64);
-                    tma_load_2d(dst + CHUNK_BYTES / 2, &p.v, bar, kv_head * 128 + 64, y + half * 64);
-                }
-            }
-        }
-    } else if (warp == MMA_WARP) {
-        // =================== MMA issuer =====================================
-        if (lane == 0) {
-            constexpr uint32_t IDESC_QK = make_idesc_bf16(TILE_M, TILE_N, false, false);
-            constexpr uint32_t IDESC_PV = make_idesc_bf16(TILE_M, HEAD_V, false, true);
-            bool alive = true;
-            auto wait_chunk = [&](int chunk) -> uint32_t {
-                const int slot = chunk % L::RING;
-                if (!mbar_wait(smem_u32(&bars->ring_full[slot]), (chunk / L::RING) & 1, abort_flag, &forward_status)) {
-                    alive = false;
-                }
-                return ring_smem + slot * CHUNK_BYTES;
-            };
-            auto release_chunk = [&](int chunk) {
-                mma_commit(smem_u32(&bars->ring_empty[chunk % L::RING]));
-            };
-            // S_i = Q_i K_j^T
-            auto issue_qk = [&](int i, int j) {
-                const uint32_t d = tmem_base + i * TILE_N;
-                for (int c = 0; c < KQ && alive; ++c) {
-                    const uint32_t k_chunk = wait_chunk(j * L::PER_TILE + c);
-                    if (!alive) {
-                        return;
-                    }
-                    tc_fence_after_sync();
-                    const uint32_t q_chunk = q_smem + (i * KQ + c) * CHUNK_BYTES;
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        mma_ss(d, make_kmajor_desc(q_chunk + k * 32), make_kmajor_desc(k_chunk + k * 32), IDESC_QK,
-                               (c | k) != 0 ? 1U : 0U);
-                    }
-                }
-                mma_commit(smem_u32(&bars->s_full[i]));
-                const bool last_user = (i == 1) || (j >= tiles[1]);
-                if (last_user) {
+    // Registers: the CTA starts with 168 per thread (12 warps).  The softmax keeps a 128-column
+    // score row in registers and spills at 168, so warps 8-11 hand registers to warps 0-7.  The
+    // two setmaxnreg instructions sit inside the role branches: after a join of branches with
+    // different limits the compiler assumes the lower one for all the code that follows.
+#ifndef REG_LO
+#define REG_LO 88
+#define REG_HI 208
+#endif
+    // The increase blocks until the CTA's pool holds the registers: what warps 8-11 release must
+    // cover what warps 0-7 request, or the kernel never starts (launch allocation: 168 each).
+    static_assert(8 * (REG_HI - 168) <= 4 * (168 - REG_LO), "register redistribution exceeds the CTA's allocation");
+    if (warp >= 8) {
+        reg_dealloc<REG_LO>();      // one instruction for the whole warpgroup; warps 10 and 11 do nothing else
+        if (warp == LOAD_WARP) {
+            // =================== TMA producer ===================================
+            if (lane == 0) {
+                auto load_q = [&](int i) {
+                    const uint32_t bar = smem_u32(&bars->q_full[i]);
+                    mbar_arrive_expect_tx(bar, KQ * CHUNK_BYTES);
+                    const int y = row0 + q_start + i * TILE_M;
                     for (int c = 0; c < KQ; ++c) {
-                        release_chunk(j * L::PER_TILE + c);
+                        const uint32_t dst = q_smem + (i * KQ + c) * CHUNK_BYTES;
+                        if (KQ == 3 && c == 2) {
+                            tma_load_2d(dst, &p.q_pe, bar, head * 64, y);
+                        } else {
+                            tma_load_2d(dst, &p.q_main, bar, head * 128 + c * 64, y);
+                        }
                     }
-                }
-            };
-            // O_i (+)= P_i V_j
-            auto issue_pv = [&](int i, int j) {
-                const uint32_t d = tmem_base + 2 * TILE_N + i * HEAD_V;
-                const uint32_t p_tmem = tmem_base + i * TILE_N;
-                for (int half = 0; half < V_CHUNKS && alive; ++half) {
-                    const uint32_t v_chunk = wait_chunk(j * L::PER_TILE + KQ + half);
-                    if (!alive) {
-                        return;
+                };
+                bool alive = true;
+                int chunk = 0;
+                // Returns the destination of ring chunk `chunk` once it is free, 0 on abort.
+                auto acquire = [&](uint32_t& bar) -> uint32_t {
+                    const int slot = chunk % L::RING;
+                    const int use = chunk / L::RING;
+                    if (use > 0 && !mbar_wait(smem_u32(&bars->ring_empty[slot]), (use - 1) & 1, abort_flag, &forward_status)) {
+                        alive = false;
+                        return 0;
                     }
-                    tc_fence_after_sync();
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        // 16 keys per step: 8 packed columns of P, 16 rows (2048 B) of V.
-                        mma_ts(d, p_tmem + half * 32 + k * 8, make_smem_desc(v_chunk + k * 2048, CHUNK_BYTES / 2, 1024), IDESC_PV,
-                               (j | half | k) != 0 ? 1U : 0U);
+                    bar = smem_u32(&bars->ring_full[slot]);
+                    mbar_arrive_expect_tx(bar, CHUNK_BYTES);
+                    ++chunk;
+                    return ring_smem + slot * CHUNK_BYTES;
+                };
+                load_q(0);
+                for (int j = 0; j < tile_count && alive; ++j) {
+                    const int y = row0 + j * TILE_N;
+                    for (int c = 0; c < KQ && alive; ++c) {
+                        uint32_t bar;
+                        const uint32_t dst = acquire(bar);
+                        if (dst == 0) {
+                            break;
+                        }
+                        if (KQ == 3 && c == 2) {
+                            tma_load_2d(dst, &p.k_pe, bar, 0, y);
+                        } else {
+                            tma_load_2d(dst, &p.k_main, bar, kv_head * 128 + c * 64, y);
+                        }
                     }
-                }
-                const bool last_user = (i == 1) || (j >= tiles[1]);
-                if (last_user) {
-                    for (int half = 0; half < V_CHUNKS; ++half) {
-                        release_chunk(j * L::PER_TILE + KQ + half);
+                    if (j == 0 && tiles[1] > 0) {
+                        load_q(1);
                     }
-                }
-            };
-
-            for (int i = 0; i < 2 && alive; ++i) {
-                if (tiles[i] > 0) {
-                    alive = mbar_wait(smem_u32(&bars->q_full[i]), 0, abort_flag, &forward_status);
-                    if (alive) {
-                        issue_qk(i, 0);
+                    for (int half = 0; half < V_CHUNKS && alive; ++half) {
+                        uint32_t bar;
+                        const uint32_t dst = acquire(bar);
+                        if (dst == 0) {
+                            break;
+                        }
+                        tma_load_2d(dst, &p.v, bar, kv_head * 128, y + half * 64);
+                        tma_load_2d(dst + CHUNK_BYTES / 2, &p.v, bar, kv_head * 128 + 64, y + half * 64);
                     }
                 }
             }
-            for (int j = 0; j < tile_count && alive; ++j) {
+        } else if (warp == MMA_WARP) {
+            // =================== MMA issuer =====================================
+            // The whole warp runs the loop (uniform control flow, uniform operands); one elected
+            // lane executes the tcgen05 instructions.  A lane-0 branch issues at well under the
+            // tensor core's rate once the softmax warps compete for the scheduler.
+            {
+                const uint32_t leader = elect_one();
+                constexpr uint32_t IDESC_QK = make_idesc_bf16(TILE_M, TILE_N, false, false);
+                constexpr uint32_t IDESC_PV = make_idesc_bf16(TILE_M, HEAD_V, false, true);
+                bool alive = true;
+                auto wait_chunk = [&](int chunk) -> uint32_t {
+                    const int slot = chunk % L::RING;
+                    if (!__all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->ring_full[slot]), (chunk / L::RING) & 1, abort_flag, &forward_status))) {
+                        alive = false;
+                    }
+                    return ring_smem + slot * CHUNK_BYTES;
+                };
+                auto release_chunk = [&](int chunk) {
+                    mma_commit_elect(smem_u32(&bars->ring_empty[chunk % L::RING]), leader);
+                };
+                // S_i = Q_i K_j^T
+                auto issue_qk = [&](int i, int j) {
+                    const uint32_t d = tmem_base + i * TILE_N;
+                    for (int c = 0; c < KQ && alive; ++c) {
+                        const uint32_t k_chunk = wait_chunk(j * L::PER_TILE + c);
+                        if (!alive) {
+                            return;
+                        }
+                        tc_fence_after_sync();
+                        const uint32_t q_chunk = q_smem + (i * KQ + c) * CHUNK_BYTES;
+    #pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            mma_ss_elect(d, make_kmajor_desc(q_chunk + k * 32), make_kmajor_desc(k_chunk + k * 32), IDESC_QK,
+                                   (c | k) != 0 ? 1U : 0U, leader);
+                        }
+                    }
+                    mma_commit_elect(smem_u32(&bars->s_full[i]), leader);
+                    const bool last_user = (i == 1) || (j >= tiles[1]);
+                    if (last_user) {
+                        for (int c = 0; c < KQ; ++c) {
+                            release_chunk(j * L::PER_TILE + c);
+                        }
+                    }
+                };
+                // O_i (+)= P_i V_j
+                auto issue_pv = [&](int i, int j) {
+                    const uint32_t d = tmem_base + 2 * TILE_N + i * HEAD_V;
+                    const uint32_t p_tmem = tmem_base + i * TILE_N;
+                    for (int half = 0; half < V_CHUNKS && alive; ++half) {
+                        const uint32_t v_chunk = wait_chunk(j * L::PER_TILE + KQ + half);
+                        if (!alive) {
+                            return;
+                        }
+                        tc_fence_after_sync();
+    #pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            // 16 keys per step: 8 packed columns of P, 16 rows (2048 B) of V.
+                            mma_ts_elect(d, p_tmem + half * 32 + k * 8, make_smem_desc(v_chunk + k * 2048, CHUNK_BYTES / 2, 1024), IDESC_PV,
+                                   (j | half | k) != 0 ? 1U : 0U, leader);
+                        }
+                    }
+                    const bool last_user = (i == 1) || (j >= tiles[1]);
+                    if (last_user) {
+                        for (int half = 0; half < V_CHUNKS; ++half) {
+                            release_chunk(j * L::PER_TILE + KQ + half);
+                        }
+                    }
+                };
+
                 for (int i = 0; i < 2 && alive; ++i) {
-                    if (j >= tiles[i]) {
-                        continue;
+                    if (tiles[i] > 0) {
+                        alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->q_full[i]), 0, abort_flag, &forward_status));
+                        if (alive) {
+                            issue_qk(i, 0);
+                        }
                     }
-                    alive = mbar_wait(smem_u32(&bars->p_full[i]), j & 1, abort_flag, &forward_status);
-                    if (!alive) {
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    issue_pv(i, j);
-                    if (!alive) {
-                        break;
-                    }
-                    if (j + 1 < tiles[i]) {
-                        issue_qk(i, j + 1);
-                    } else {
-                        mma_commit(smem_u32(&bars->s_full[i]));   // O_i is final
+                }
+                for (int j = 0; j < tile_count && alive; ++j) {
+                    for (int i = 0; i < 2 && alive; ++i) {
+                        if (j >= tiles[i]) {
+                            continue;
+                        }
+                        alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->p_full[i]), j & 1, abort_flag, &forward_status));
+                        if (!alive) {
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        issue_pv(i, j);
+                        if (!alive) {
+                            break;
+                        }
+                        if (j + 1 < tiles[i]) {
+                            issue_qk(i, j + 1);
+                        } else {
+                            mma_commit_elect(smem_u32(&bars->s_full[i]), leader);   // O_i is final
+                        }
                     }
                 }
             }
         }
     } else {
         // =================== softmax + epilogue =============================
+        reg_alloc<REG_HI>();
         const int i = warp / 4;                       // tile of this warpgroup
         const int r = threadIdx.x % TILE_M;           // row inside the tile
         const uint32_t lane_base = static_cast<uint32_t>((warp % 4) * 32) << 16;
