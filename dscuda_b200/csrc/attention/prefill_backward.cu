@@ -261,13 +261,15 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dq_kernel(const __grid_co
             }
         }
     } else if (warp == MMA_WARP) {
-        if (lane == 0) {
+        // Whole warp, uniform control flow; the elected lane executes the tcgen05 instructions.
+        {
+            const uint32_t leader = elect_one();
             constexpr uint32_t IDESC_SCORE = make_idesc_bf16(BIG, SUB, false, false);
             constexpr uint32_t IDESC_DQ = make_idesc_bf16(BIG, 192, false, true);
-            bool alive = mbar_wait(smem_u32(&bars->resident_full), 0, abort_flag, &backward_status);
+            bool alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->resident_full), 0, abort_flag, &backward_status));
             auto issue_scores = [&](int j) {
                 const int stage = j % STAGES;
-                alive = mbar_wait(smem_u32(&bars->stage_full[stage]), (j / STAGES) & 1, abort_flag, &backward_status);
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->stage_full[stage]), (j / STAGES) & 1, abort_flag, &backward_status));
                 if (!alive) {
                     return;
                 }
@@ -279,19 +281,19 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dq_kernel(const __grid_co
                 for (int c = 0; c < 3; ++c) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        mma_ss(s_tmem, make_kmajor_desc(q_smem + c * BIG_CHUNK + k * 32), make_kmajor_desc(k_smem + c * SUB_CHUNK + k * 32),
-                               IDESC_SCORE, (c | k) != 0 ? 1U : 0U);
+                        mma_ss_elect(s_tmem, make_kmajor_desc(q_smem + c * BIG_CHUNK + k * 32), make_kmajor_desc(k_smem + c * SUB_CHUNK + k * 32),
+                               IDESC_SCORE, (c | k) != 0 ? 1U : 0U, leader);
                     }
                 }
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        mma_ss(s_tmem + 64, make_kmajor_desc(do_smem + c * BIG_CHUNK + k * 32),
-                               make_kmajor_desc(v_smem + c * SUB_CHUNK + k * 32), IDESC_SCORE, (c | k) != 0 ? 1U : 0U);
+                        mma_ss_elect(s_tmem + 64, make_kmajor_desc(do_smem + c * BIG_CHUNK + k * 32),
+                               make_kmajor_desc(v_smem + c * SUB_CHUNK + k * 32), IDESC_SCORE, (c | k) != 0 ? 1U : 0U, leader);
                     }
                 }
-                mma_commit(smem_u32(&bars->mma_a[j & 1]));
+                mma_commit_elect(smem_u32(&bars->mma_a[j & 1]), leader);
             };
             if (alive) {
                 issue_scores(0);
@@ -303,7 +305,7 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dq_kernel(const __grid_co
                         break;
                     }
                 }
-                alive = mbar_wait(smem_u32(&bars->soft_a[j & 1]), (j >> 1) & 1, abort_flag, &backward_status);
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->soft_a[j & 1]), (j >> 1) & 1, abort_flag, &backward_status));
                 if (!alive) {
                     break;
                 }
@@ -313,13 +315,13 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dq_kernel(const __grid_co
                 const uint32_t ds_tmem = tmem_base + (j & 1) * 128 + 64;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    mma_ts(tmem_base + TMEM_DQ, ds_tmem + k * 8, make_smem_desc(k_smem + k * 2048, SUB_CHUNK, 1024), IDESC_DQ,
-                           (j | k) != 0 ? 1U : 0U);
+                    mma_ts_elect(tmem_base + TMEM_DQ, ds_tmem + k * 8, make_smem_desc(k_smem + k * 2048, SUB_CHUNK, 1024), IDESC_DQ,
+                           (j | k) != 0 ? 1U : 0U, leader);
                 }
-                mma_commit(smem_u32(&bars->stage_empty[stage]));
+                mma_commit_elect(smem_u32(&bars->stage_empty[stage]), leader);
             }
             if (alive) {
-                mma_commit(smem_u32(&bars->final_full));
+                mma_commit_elect(smem_u32(&bars->final_full), leader);
             }
         }
     } else {
@@ -495,16 +497,18 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
             }
         }
     } else if (warp == MMA_WARP) {
-        if (lane == 0) {
+        // Whole warp, uniform control flow; the elected lane executes the tcgen05 instructions.
+        {
+            const uint32_t leader = elect_one();
             constexpr uint32_t IDESC_SCORE = make_idesc_bf16(BIG, SUB, false, false);
             constexpr uint32_t IDESC_DV = make_idesc_bf16(BIG, 128, false, true);
             constexpr uint32_t IDESC_DK = make_idesc_bf16(BIG, 192, false, true);
-            bool alive = mbar_wait(smem_u32(&bars->resident_full), 0, abort_flag, &backward_status);
+            bool alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->resident_full), 0, abort_flag, &backward_status));
             auto x_buffer = [&](int index) -> uint32_t { return tmem_base + TMEM_X + (index % 3) * 64; };
             // S^T(t) = K Q_t^T
             auto issue_st = [&](int t) {
                 const int stage = t % STAGES;
-                alive = mbar_wait(smem_u32(&bars->stage_full[stage]), (t / STAGES) & 1, abort_flag, &backward_status);
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->stage_full[stage]), (t / STAGES) & 1, abort_flag, &backward_status));
                 if (!alive) {
                     return;
                 }
@@ -514,11 +518,11 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
                 for (int c = 0; c < 3; ++c) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        mma_ss(x_buffer(2 * t), make_kmajor_desc(k_smem + c * BIG_CHUNK + k * 32),
-                               make_kmajor_desc(q_smem + c * SUB_CHUNK + k * 32), IDESC_SCORE, (c | k) != 0 ? 1U : 0U);
+                        mma_ss_elect(x_buffer(2 * t), make_kmajor_desc(k_smem + c * BIG_CHUNK + k * 32),
+                               make_kmajor_desc(q_smem + c * SUB_CHUNK + k * 32), IDESC_SCORE, (c | k) != 0 ? 1U : 0U, leader);
                     }
                 }
-                mma_commit(smem_u32(&bars->mma_a[t & 1]));
+                mma_commit_elect(smem_u32(&bars->mma_a[t & 1]), leader);
             };
             // dP^T(t) = V dO_t^T   (the stage is already known to be full)
             auto issue_dpt = [&](int t) {
@@ -527,11 +531,11 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
                 for (int c = 0; c < 2; ++c) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        mma_ss(x_buffer(2 * t + 1), make_kmajor_desc(v_smem + c * BIG_CHUNK + k * 32),
-                               make_kmajor_desc(do_smem + c * SUB_CHUNK + k * 32), IDESC_SCORE, (c | k) != 0 ? 1U : 0U);
+                        mma_ss_elect(x_buffer(2 * t + 1), make_kmajor_desc(v_smem + c * BIG_CHUNK + k * 32),
+                               make_kmajor_desc(do_smem + c * SUB_CHUNK + k * 32), IDESC_SCORE, (c | k) != 0 ? 1U : 0U, leader);
                     }
                 }
-                mma_commit(smem_u32(&bars->mma_b[t & 1]));
+                mma_commit_elect(smem_u32(&bars->mma_b[t & 1]), leader);
             };
             if (alive) {
                 issue_st(0);
@@ -548,7 +552,7 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
                         break;
                     }
                 }
-                alive = mbar_wait(smem_u32(&bars->soft_a[t & 1]), parity, abort_flag, &backward_status);
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->soft_a[t & 1]), parity, abort_flag, &backward_status));
                 if (!alive) {
                     break;
                 }
@@ -558,13 +562,13 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
                 // dV += P^T dO_t
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    mma_ts(tmem_base + TMEM_DV, x_buffer(2 * t) + k * 8, make_smem_desc(do_smem + k * 2048, SUB_CHUNK, 1024), IDESC_DV,
-                           (t | k) != 0 ? 1U : 0U);
+                    mma_ts_elect(tmem_base + TMEM_DV, x_buffer(2 * t) + k * 8, make_smem_desc(do_smem + k * 2048, SUB_CHUNK, 1024), IDESC_DV,
+                           (t | k) != 0 ? 1U : 0U, leader);
                 }
                 if (t + 1 < tile_count) {
                     issue_dpt(t + 1);
                 }
-                alive = mbar_wait(smem_u32(&bars->soft_b[t & 1]), parity, abort_flag, &backward_status);
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->soft_b[t & 1]), parity, abort_flag, &backward_status));
                 if (!alive) {
                     break;
                 }
@@ -572,13 +576,13 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
                 // dK += dS^T Q_t
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    mma_ts(tmem_base + TMEM_DK, x_buffer(2 * t + 1) + k * 8, make_smem_desc(q_smem + k * 2048, SUB_CHUNK, 1024), IDESC_DK,
-                           (t | k) != 0 ? 1U : 0U);
+                    mma_ts_elect(tmem_base + TMEM_DK, x_buffer(2 * t + 1) + k * 8, make_smem_desc(q_smem + k * 2048, SUB_CHUNK, 1024), IDESC_DK,
+                           (t | k) != 0 ? 1U : 0U, leader);
                 }
-                mma_commit(smem_u32(&bars->stage_empty[stage]));
+                mma_commit_elect(smem_u32(&bars->stage_empty[stage]), leader);
             }
             if (alive) {
-                mma_commit(smem_u32(&bars->final_full));
+                mma_commit_elect(smem_u32(&bars->final_full), leader);
             }
         }
     } else {
