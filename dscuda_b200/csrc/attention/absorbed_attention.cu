@@ -435,7 +435,9 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
         }
     } else if (warp == MMA_WARP) {
         // =================== MMA issuer =====================================
-        if (lane == 0) {
+        // Whole warp, uniform control flow; the elected lane executes the tcgen05 instructions.
+        {
+            const uint32_t leader = elect_one();
             constexpr uint32_t IDESC_QK = make_idesc_bf16(ROWS, KEYS, false, false);
             constexpr uint32_t IDESC_PV = make_idesc_bf16(ROWS, HALF_V, false, true);
             constexpr uint32_t HI = smem_desc_hi(1024);
@@ -448,7 +450,7 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
             // A group of tile `tile`: five slices with Q from shared memory, starts the accumulator
             auto issue_a_part = [&](int tile) {
                 const int slot_a = tile % A_SLOTS;
-                alive = mbar_wait(smem_u32(&bars->full_a[slot_a]), (tile / A_SLOTS) & 1, abort_flag, &absorbed_status);
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->full_a[slot_a]), (tile / A_SLOTS) & 1, abort_flag, &absorbed_status));
                 if (!alive) {
                     return;
                 }
@@ -459,15 +461,15 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                     const uint32_t k_lo = a_lo + (slot_a * A_CHUNKS + i) * CHUNK_LO;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        mma_ss_split(s_tmem, q_lo + i * (Q_CHUNK_BYTES >> 4) + 2 * k, HI, k_lo + 2 * k, HI, IDESC_QK, (i | k) != 0 ? 1U : 0U);
+                        mma_ss_split_elect(s_tmem, q_lo + i * (Q_CHUNK_BYTES >> 4) + 2 * k, HI, k_lo + 2 * k, HI, IDESC_QK, (i | k) != 0 ? 1U : 0U, leader);
                     }
                 }
-                mma_commit(smem_u32(&bars->empty_a[slot_a]));
+                mma_commit_elect(smem_u32(&bars->empty_a[slot_a]), leader);
             };
             // B group of tile `tile`: four slices with Q from tensor memory, completes S
             auto issue_b_part = [&](int tile) {
                 const int slot_b = tile % B_SLOTS;
-                alive = mbar_wait(smem_u32(&bars->full_b[slot_b]), (tile / B_SLOTS) & 1, abort_flag, &absorbed_status);
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->full_b[slot_b]), (tile / B_SLOTS) & 1, abort_flag, &absorbed_status));
                 if (!alive) {
                     return;
                 }
@@ -478,16 +480,16 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                     const uint32_t k_lo = b_lo + (slot_b * B_CHUNKS + i) * CHUNK_LO;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        mma_ts_split(s_tmem, tmem_base + TMEM_Q + i * 32 + k * 8, k_lo + 2 * k, HI, IDESC_QK, 1U);
+                        mma_ts_split_elect(s_tmem, tmem_base + TMEM_Q + i * 32 + k * 8, k_lo + 2 * k, HI, IDESC_QK, 1U, leader);
                     }
                 }
-                mma_commit(smem_u32(&bars->s_full[tile & 1]));
+                mma_commit_elect(smem_u32(&bars->s_full[tile & 1]), leader);
             };
             while (alive && next_segment(p, schedule, walker, seg, pair, pairs)) {
                 const int tile_count = seg.tile_end - seg.tile_begin;
                 const uint32_t seg_parity = segment_index & 1;
-                alive = mbar_wait(smem_u32(&bars->q_full), seg_parity, abort_flag, &absorbed_status) &&
-                        mbar_wait(smem_u32(&bars->q_tmem_ready), seg_parity, abort_flag, &absorbed_status);
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->q_full), seg_parity, abort_flag, &absorbed_status) &&
+                                                    mbar_wait(smem_u32(&bars->q_tmem_ready), seg_parity, abort_flag, &absorbed_status));
                 if (alive) {
                     tc_fence_after_sync();
                     issue_a_part(tile_index);
@@ -507,7 +509,7 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                     }
                     STAMP(1, tile, 4);
                     // ---- O (+)= P V ----
-                    alive = mbar_wait(smem_u32(&bars->p_full[tile & 1]), (tile >> 1) & 1, abort_flag, &absorbed_status);
+                    alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->p_full[tile & 1]), (tile >> 1) & 1, abort_flag, &absorbed_status));
                     if (!alive) {
                         break;
                     }
@@ -516,17 +518,17 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                     const uint32_t p_tmem = tmem_base + TMEM_S + (tile & 1) * KEYS;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        mma_ts_split(tmem_base + TMEM_O, p_tmem + k * 8, v_lo + slot_b * B_CHUNKS * CHUNK_LO + k * (2048 >> 4), HI, IDESC_PV,
-                                     (j | k) != 0 ? 1U : 0U);
+                        mma_ts_split_elect(tmem_base + TMEM_O, p_tmem + k * 8, v_lo + slot_b * B_CHUNKS * CHUNK_LO + k * (2048 >> 4), HI, IDESC_PV,
+                                     (j | k) != 0 ? 1U : 0U, leader);
                     }
-                    mma_commit(smem_u32(&bars->empty_b[slot_b]));
+                    mma_commit_elect(smem_u32(&bars->empty_b[slot_b]), leader);
                     STAMP(1, tile, 6);
                     if (j + 1 < tile_count) {
                         issue_b_part(tile + 1);
                     }
                 }
                 if (alive) {
-                    mma_commit(smem_u32(&bars->o_final));
+                    mma_commit_elect(smem_u32(&bars->o_final), leader);
                 }
                 tile_index += tile_count;
                 segment_index += 1;
