@@ -190,11 +190,57 @@ __global__ void __launch_bounds__(256) convert_dk_pe_kernel(__nv_bfloat16* dk_pe
 }
 
 // ---------------------------------------------------------------------------
-// dQ kernel: stationary 128 query rows (Q 3 chunks, dO 2 chunks), streamed
-// 64-key tiles (K 3 chunks, V 2 chunks).
-// Tensor memory: set g in {0,1}: S at 128g, dP at 128g+64; dQ at 256..447.
+// dQ kernel: stationary 128 query rows, streamed 128-key tiles.
+//
+// Shared memory: Q (3 chunks of [128 rows x 64 bf16], 48 KB), a ring of three K
+// tiles (3 chunks each, 144 KB) and one V slot (2 chunks, 32 KB) that first
+// holds dO.  K(j) is read by S(j) and again by dQ(j), which runs a tile and a
+// half later, hence three slots; V(j) is only read by dP(j).
+// Tensor memory: S at 0..127, dP at 128..255 (dS overwrites it as bf16: keys
+// 0-63 at 128..159, keys 64-127 at 192..223), dQ at 256..447, dO (bf16, an MMA
+// A operand) at 448..511.
+//
+// Tensor-core order in steady state: S(j+1) | dQ(j) | dP(j+1).  The softmax is
+// split in two stages so that one (S, dP) pair is enough: stage 1 copies S(j) to
+// registers (S may then be overwritten by S(j+1)) and computes P while dQ(j-1)
+// and dP(j) run; stage 2 reads dP(j), writes dS(j) while S(j+1) runs.  All 256
+// softmax threads work on the same tile: thread = (row, half of the keys).
 // ---------------------------------------------------------------------------
+namespace dqk {
+constexpr int KEYS = 128;
+constexpr int CHUNK = 128 * 128;                 // [128 rows x 64 bf16], 16 KB
+constexpr int Q_BYTES = 3 * CHUNK;
+constexpr int K_TILE = 3 * CHUNK;
+constexpr int K_SLOTS = 3;
+constexpr int V_TILE = 2 * CHUNK;
+constexpr int BAR_BYTES = 1024;
+constexpr int SMEM_BYTES = Q_BYTES + K_SLOTS * K_TILE + V_TILE + BAR_BYTES;
+constexpr uint32_t TMEM_S = 0;
+constexpr uint32_t TMEM_DP = 128;
+constexpr uint32_t TMEM_DQ = 256;
+constexpr uint32_t TMEM_DO = 448;
+static_assert(SMEM_BYTES <= 227 * 1024, "dQ kernel shared memory");
+
+struct Barriers {
+    uint64_t resident_full;     // Q and dO have landed
+    uint64_t do_copied;         // 256 softmax threads: dO is in tensor memory, the V slot is free
+    uint64_t k_full[K_SLOTS];
+    uint64_t k_empty[K_SLOTS];
+    uint64_t v_full;
+    uint64_t v_empty;
+    uint64_t s_full;            // tensor core -> softmax: S(j) complete
+    uint64_t dp_full;           // tensor core -> softmax: dP(j) complete
+    uint64_t s_free;            // 256 softmax threads: S(j) is in registers
+    uint64_t ds_full;           // 256 softmax threads: dS(j) stored
+    uint64_t final_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+static_assert(sizeof(Barriers) <= BAR_BYTES, "barrier block too large");
+}  // namespace dqk
+
 __global__ void __launch_bounds__(THREADS, 1) backward_dq_kernel(const __grid_constant__ BackwardParams p) {
+    using namespace dqk;
     extern __shared__ uint8_t smem_raw[];
     if (*reinterpret_cast<volatile int*>(&backward_status) != 0) {
         return;
@@ -208,20 +254,41 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dq_kernel(const __grid_co
     block = blocks_in_sequence - 1 - block;            // longest first
     const int q_start = block * BIG;
     const int kv_end = min(length, q_start + BIG);
-    const int tile_count = (kv_end + SUB - 1) / SUB;
+    const int tile_count = (kv_end + KEYS - 1) / KEYS;
 
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023U) & ~1023U;
-    uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t q_smem = smem_base;                          // 3 chunks
-    const uint32_t do_smem = smem_base + 3 * BIG_CHUNK;         // 2 chunks
-    const uint32_t stage_smem = smem_base + RESIDENT_BYTES;
-    BackwardBarriers* bars = reinterpret_cast<BackwardBarriers*>(smem_aligned + RESIDENT_BYTES + STAGES * STAGE_BYTES);
+    // The layout uses all of the CTA's shared memory, so there is no room to realign: the
+    // dynamic region starts 1024-byte aligned when the kernel has no static shared memory.
+    const uint32_t smem_base = smem_u32(smem_raw);
+    if ((smem_base & 1023U) != 0U) {
+        if (threadIdx.x == 0) {
+            atomicExch(&backward_status, STATUS_SMEM_MISALIGNED);
+        }
+        return;
+    }
+    const uint32_t q_smem = smem_base;
+    const uint32_t k_ring = smem_base + Q_BYTES;
+    const uint32_t v_smem = k_ring + K_SLOTS * K_TILE;
+    Barriers* bars = reinterpret_cast<Barriers*>(smem_raw + Q_BYTES + K_SLOTS * K_TILE + V_TILE);
     volatile int* abort_flag = &bars->abort_flag;
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
 
     if (threadIdx.x == 0) {
-        init_barriers(bars, 1);
+        mbar_init(smem_u32(&bars->resident_full), 1);
+        mbar_init(smem_u32(&bars->do_copied), 256);
+        for (int i = 0; i < K_SLOTS; ++i) {
+            mbar_init(smem_u32(&bars->k_full[i]), 1);
+            mbar_init(smem_u32(&bars->k_empty[i]), 1);
+        }
+        mbar_init(smem_u32(&bars->v_full), 1);
+        mbar_init(smem_u32(&bars->v_empty), 1);
+        mbar_init(smem_u32(&bars->s_full), 1);
+        mbar_init(smem_u32(&bars->dp_full), 1);
+        mbar_init(smem_u32(&bars->s_free), 256);
+        mbar_init(smem_u32(&bars->ds_full), 256);
+        mbar_init(smem_u32(&bars->final_full), 1);
+        bars->abort_flag = 0;
+        mbar_init_fence();
     }
     if (warp == MMA_WARP) {
         tmem_alloc(smem_u32(&bars->tmem_base), TMEM_COLUMNS);
@@ -231,140 +298,216 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dq_kernel(const __grid_co
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
-    constexpr uint32_t TMEM_DQ = 256;
 
     if (warp == LOAD_WARP) {
         if (lane == 0) {
-            const uint32_t bar = smem_u32(&bars->resident_full);
-            mbar_arrive_expect_tx(bar, RESIDENT_BYTES);
-            const int y = row0 + q_start;
-            tma_load_2d(q_smem, &p.q_main_big, bar, head * 128, y);
-            tma_load_2d(q_smem + BIG_CHUNK, &p.q_main_big, bar, head * 128 + 64, y);
-            tma_load_2d(q_smem + 2 * BIG_CHUNK, &p.q_pe_big, bar, head * 64, y);
-            tma_load_2d(do_smem, &p.do_big, bar, head * 128, y);
-            tma_load_2d(do_smem + BIG_CHUNK, &p.do_big, bar, head * 128 + 64, y);
-            for (int j = 0; j < tile_count; ++j) {
-                const int stage = j % STAGES;
-                const int use = j / STAGES;
-                if (use > 0 && !mbar_wait(smem_u32(&bars->stage_empty[stage]), (use - 1) & 1, abort_flag, &backward_status)) {
-                    break;
+            bool alive = true;
+            {
+                const uint32_t bar = smem_u32(&bars->resident_full);
+                mbar_arrive_expect_tx(bar, Q_BYTES + V_TILE);
+                const int y = row0 + q_start;
+                tma_load_2d(q_smem, &p.q_main_big, bar, head * 128, y);
+                tma_load_2d(q_smem + CHUNK, &p.q_main_big, bar, head * 128 + 64, y);
+                tma_load_2d(q_smem + 2 * CHUNK, &p.q_pe_big, bar, head * 64, y);
+                tma_load_2d(v_smem, &p.do_big, bar, head * 128, y);
+                tma_load_2d(v_smem + CHUNK, &p.do_big, bar, head * 128 + 64, y);
+            }
+            auto load_k = [&](int j) {
+                const int slot = j % K_SLOTS;
+                const int use = j / K_SLOTS;
+                if (use > 0 && !mbar_wait(smem_u32(&bars->k_empty[slot]), (use - 1) & 1, abort_flag, &backward_status)) {
+                    alive = false;
+                    return;
                 }
-                const uint32_t full = smem_u32(&bars->stage_full[stage]);
-                mbar_arrive_expect_tx(full, STAGE_BYTES);
-                const uint32_t dst = stage_smem + stage * STAGE_BYTES;
-                const int ky = row0 + j * SUB;
-                tma_load_2d(dst, &p.k_main_sub, full, head * 128, ky);
-                tma_load_2d(dst + SUB_CHUNK, &p.k_main_sub, full, head * 128 + 64, ky);
-                tma_load_2d(dst + 2 * SUB_CHUNK, &p.k_pe_sub, full, 0, ky);
-                tma_load_2d(dst + 3 * SUB_CHUNK, &p.v_sub, full, head * 128, ky);
-                tma_load_2d(dst + 4 * SUB_CHUNK, &p.v_sub, full, head * 128 + 64, ky);
+                const uint32_t full = smem_u32(&bars->k_full[slot]);
+                mbar_arrive_expect_tx(full, K_TILE);
+                const uint32_t dst = k_ring + slot * K_TILE;
+                const int ky = row0 + j * KEYS;
+                tma_load_2d(dst, &p.k_main_big, full, head * 128, ky);
+                tma_load_2d(dst + CHUNK, &p.k_main_big, full, head * 128 + 64, ky);
+                tma_load_2d(dst + 2 * CHUNK, &p.k_pe_big, full, 0, ky);
+            };
+            auto load_v = [&](int j) {
+                // the slot is free once dO has been copied out (first tile) or dP(j-1) has run
+                const bool ready = j == 0 ? mbar_wait(smem_u32(&bars->do_copied), 0, abort_flag, &backward_status)
+                                          : mbar_wait(smem_u32(&bars->v_empty), (j - 1) & 1, abort_flag, &backward_status);
+                if (!ready) {
+                    alive = false;
+                    return;
+                }
+                const uint32_t full = smem_u32(&bars->v_full);
+                mbar_arrive_expect_tx(full, V_TILE);
+                const int ky = row0 + j * KEYS;
+                tma_load_2d(v_smem, &p.v_big, full, head * 128, ky);
+                tma_load_2d(v_smem + CHUNK, &p.v_big, full, head * 128 + 64, ky);
+            };
+            // K(j) becomes loadable after dQ(j-3), V(j-1) right after that (after dP(j-2)).
+            for (int j = 0; j < tile_count && alive; ++j) {
+                load_k(j);
+                if (j >= 1 && alive) {
+                    load_v(j - 1);
+                }
+            }
+            if (alive) {
+                load_v(tile_count - 1);
             }
         }
     } else if (warp == MMA_WARP) {
         // Whole warp, uniform control flow; the elected lane executes the tcgen05 instructions.
-        {
-            const uint32_t leader = elect_one();
-            constexpr uint32_t IDESC_SCORE = make_idesc_bf16(BIG, SUB, false, false);
-            constexpr uint32_t IDESC_DQ = make_idesc_bf16(BIG, 192, false, true);
-            bool alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->resident_full), 0, abort_flag, &backward_status));
-            auto issue_scores = [&](int j) {
-                const int stage = j % STAGES;
-                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->stage_full[stage]), (j / STAGES) & 1, abort_flag, &backward_status));
-                if (!alive) {
-                    return;
-                }
-                tc_fence_after_sync();
-                const uint32_t k_smem = stage_smem + stage * STAGE_BYTES;
-                const uint32_t v_smem = k_smem + 3 * SUB_CHUNK;
-                const uint32_t s_tmem = tmem_base + (j & 1) * 128;
-#pragma unroll
-                for (int c = 0; c < 3; ++c) {
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        mma_ss_elect(s_tmem, make_kmajor_desc(q_smem + c * BIG_CHUNK + k * 32), make_kmajor_desc(k_smem + c * SUB_CHUNK + k * 32),
-                               IDESC_SCORE, (c | k) != 0 ? 1U : 0U, leader);
-                    }
-                }
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        mma_ss_elect(s_tmem + 64, make_kmajor_desc(do_smem + c * BIG_CHUNK + k * 32),
-                               make_kmajor_desc(v_smem + c * SUB_CHUNK + k * 32), IDESC_SCORE, (c | k) != 0 ? 1U : 0U, leader);
-                    }
-                }
-                mma_commit_elect(smem_u32(&bars->mma_a[j & 1]), leader);
-            };
-            if (alive) {
-                issue_scores(0);
+        const uint32_t leader = elect_one();
+        constexpr uint32_t IDESC_SCORE = make_idesc_bf16(BIG, KEYS, false, false);
+        constexpr uint32_t IDESC_DQ = make_idesc_bf16(BIG, 192, false, true);
+        bool alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->resident_full), 0, abort_flag, &backward_status));
+        // S(j) = Q K_j^T
+        auto issue_s = [&](int j) {
+            const int slot = j % K_SLOTS;
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->k_full[slot]), (j / K_SLOTS) & 1, abort_flag, &backward_status));
+            if (alive && j > 0) {
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->s_free), (j - 1) & 1, abort_flag, &backward_status));
             }
-            for (int j = 0; j < tile_count && alive; ++j) {
-                if (j + 1 < tile_count) {
-                    issue_scores(j + 1);
-                    if (!alive) {
-                        break;
-                    }
+            if (!alive) {
+                return;
+            }
+            tc_fence_after_sync();
+            const uint32_t k_smem = k_ring + slot * K_TILE;
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    mma_ss_elect(tmem_base + TMEM_S, make_kmajor_desc(q_smem + c * CHUNK + k * 32), make_kmajor_desc(k_smem + c * CHUNK + k * 32),
+                                 IDESC_SCORE, (c | k) != 0 ? 1U : 0U, leader);
                 }
-                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->soft_a[j & 1]), (j >> 1) & 1, abort_flag, &backward_status));
+            }
+            mma_commit_elect(smem_u32(&bars->s_full), leader);
+        };
+        // dP(j) = dO V_j^T, dO from tensor memory
+        auto issue_dp = [&](int j) {
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->v_full), j & 1, abort_flag, &backward_status));
+            if (!alive) {
+                return;
+            }
+            tc_fence_after_sync();
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    mma_ts_elect(tmem_base + TMEM_DP, tmem_base + TMEM_DO + c * 32 + k * 8, make_kmajor_desc(v_smem + c * CHUNK + k * 32), IDESC_SCORE,
+                                 (c | k) != 0 ? 1U : 0U, leader);
+                }
+            }
+            mma_commit_elect(smem_u32(&bars->v_empty), leader);
+            mma_commit_elect(smem_u32(&bars->dp_full), leader);
+        };
+        if (alive) {
+            issue_s(0);
+        }
+        if (alive) {
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->do_copied), 0, abort_flag, &backward_status));
+        }
+        if (alive) {
+            tc_fence_after_sync();
+            issue_dp(0);
+        }
+        for (int j = 0; j < tile_count && alive; ++j) {
+            if (j + 1 < tile_count) {
+                issue_s(j + 1);
                 if (!alive) {
                     break;
                 }
-                tc_fence_after_sync();
-                const int stage = j % STAGES;
-                const uint32_t k_smem = stage_smem + stage * STAGE_BYTES;
-                const uint32_t ds_tmem = tmem_base + (j & 1) * 128 + 64;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    mma_ts_elect(tmem_base + TMEM_DQ, ds_tmem + k * 8, make_smem_desc(k_smem + k * 2048, SUB_CHUNK, 1024), IDESC_DQ,
-                           (j | k) != 0 ? 1U : 0U, leader);
-                }
-                mma_commit_elect(smem_u32(&bars->stage_empty[stage]), leader);
             }
-            if (alive) {
-                mma_commit_elect(smem_u32(&bars->final_full), leader);
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->ds_full), j & 1, abort_flag, &backward_status));
+            if (!alive) {
+                break;
+            }
+            tc_fence_after_sync();
+            // dQ += dS(j) K_j: 16 keys per step, the three 64-column blocks of K are 16 KB apart
+            const uint32_t k_smem = k_ring + (j % K_SLOTS) * K_TILE;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t ds_tmem = tmem_base + TMEM_DP + (k / 4) * 64 + (k % 4) * 8;
+                mma_ts_elect(tmem_base + TMEM_DQ, ds_tmem, make_smem_desc(k_smem + k * 2048, CHUNK, 1024), IDESC_DQ, (j | k) != 0 ? 1U : 0U, leader);
+            }
+            mma_commit_elect(smem_u32(&bars->k_empty[j % K_SLOTS]), leader);
+            if (j + 1 < tile_count) {
+                issue_dp(j + 1);
             }
         }
+        if (alive) {
+            mma_commit_elect(smem_u32(&bars->final_full), leader);
+        }
     } else {
-        const int group = warp / 4;
+        // =================== softmax: thread = (row, half of the keys) =======
+        const int half = warp / 4;
         const int r = threadIdx.x % BIG;
         const uint32_t lane_base = static_cast<uint32_t>((warp % 4) * 32) << 16;
         const int q_pos = q_start + r;
         const int q_safe = min(q_pos, length - 1);
         const float lse2 = p.lse[lse_offset + q_safe] * LOG2E;
         const float delta = p.delta[lse_offset + q_safe];
-        bool alive = true;
-        for (int j = group; j < tile_count; j += 2) {
-            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->mma_a[group]), (j >> 1) & 1, abort_flag, &backward_status));
+        bool alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->resident_full), 0, abort_flag, &backward_status));
+        if (alive) {
+            // dO chunk `half`, row r -> 32 packed columns of tensor memory (undo the 128-byte swizzle)
+            uint32_t values[32];
+            const uint8_t* row = smem_raw + Q_BYTES + K_SLOTS * K_TILE + half * CHUNK + r * 128;
+#pragma unroll
+            for (int unit = 0; unit < 8; ++unit) {
+                const uint4 v = *reinterpret_cast<const uint4*>(row + ((unit ^ (r & 7)) * 16));
+                values[unit * 4 + 0] = v.x;
+                values[unit * 4 + 1] = v.y;
+                values[unit * 4 + 2] = v.z;
+                values[unit * 4 + 3] = v.w;
+            }
+            tmem_st_x32(tmem_base + lane_base + TMEM_DO + half * 32, values);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bars->do_copied));
+        }
+        const uint32_t s_tmem = tmem_base + lane_base + TMEM_S + half * 64;
+        const uint32_t dp_tmem = tmem_base + lane_base + TMEM_DP + half * 64;
+        for (int j = 0; j < tile_count && alive; ++j) {
+            // ---- stage 1: S -> registers, P ----
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->s_full), j & 1, abort_flag, &backward_status));
             if (!alive) {
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t s_tmem = tmem_base + lane_base + group * 128;
-            uint32_t sb[SUB], dp[SUB];
+            uint32_t sb[64];
             tmem_ld_x32(s_tmem, sb);
             tmem_ld_x32(s_tmem + 32, sb + 32);
-            tmem_ld_x32(s_tmem + 64, dp);
-            tmem_ld_x32(s_tmem + 96, dp + 32);
             tmem_wait_ld();
-            const int key0 = j * SUB;
-            const bool masked = key0 + SUB - 1 > q_start;
-            uint32_t packed[SUB / 2];
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bars->s_free));
+            const int key0 = j * KEYS + half * 64;
+            const bool masked = key0 + 63 > q_start;
+            float prob[64];          // P * scale
 #pragma unroll
-            for (int n = 0; n < SUB; n += 2) {
-                float p0 = exp2_approx(fmaf(__uint_as_float(sb[n]), p.scale_log2, -lse2));
-                float p1 = exp2_approx(fmaf(__uint_as_float(sb[n + 1]), p.scale_log2, -lse2));
+            for (int n = 0; n < 64; ++n) {
+                float value = exp2_approx(fmaf(__uint_as_float(sb[n]), p.scale_log2, -lse2)) * p.scale;
                 if (masked) {
-                    p0 = key0 + n <= q_pos ? p0 : 0.0F;
-                    p1 = key0 + n + 1 <= q_pos ? p1 : 0.0F;
+                    value = key0 + n <= q_pos ? value : 0.0F;
                 }
-                const float d0 = p0 * (__uint_as_float(dp[n]) - delta) * p.scale;
-                const float d1 = p1 * (__uint_as_float(dp[n + 1]) - delta) * p.scale;
+                prob[n] = value;
+            }
+            // ---- stage 2: dS = P (dP - delta) scale ----
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->dp_full), j & 1, abort_flag, &backward_status));
+            if (!alive) {
+                break;
+            }
+            tc_fence_after_sync();
+            tmem_ld_x32(dp_tmem, sb);
+            tmem_ld_x32(dp_tmem + 32, sb + 32);
+            tmem_wait_ld();
+            uint32_t packed[32];
+#pragma unroll
+            for (int n = 0; n < 64; n += 2) {
+                const float d0 = prob[n] * (__uint_as_float(sb[n]) - delta);
+                const float d1 = prob[n + 1] * (__uint_as_float(sb[n + 1]) - delta);
                 packed[n / 2] = pack_bf16x2(d0, d1);
             }
-            tmem_st_x32(s_tmem + 64, packed);
+            tmem_st_x32(dp_tmem, packed);
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(smem_u32(&bars->soft_a[group]));
+            mbar_arrive(smem_u32(&bars->ds_full));
         }
         if (alive) {
             alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->final_full), 0, abort_flag, &backward_status));
@@ -372,11 +515,11 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dq_kernel(const __grid_co
         if (alive) {
             tc_fence_after_sync();
             const bool valid = q_pos < length;
-            __nv_bfloat16* dq_row = p.dq + (static_cast<size_t>(row0 + q_pos) * p.heads + head) * 192 + group * 96;
+            __nv_bfloat16* dq_row = p.dq + (static_cast<size_t>(row0 + q_pos) * p.heads + head) * 192 + half * 96;
 #pragma unroll
             for (int c = 0; c < 3; ++c) {
                 uint32_t values[32];
-                tmem_ld_x32(tmem_base + lane_base + TMEM_DQ + group * 96 + c * 32, values);
+                tmem_ld_x32(tmem_base + lane_base + TMEM_DQ + half * 96 + c * 32, values);
                 tmem_wait_ld();
                 if (valid) {
                     store_bf16_row(dq_row + c * 32, values, 32, 1.0F);
@@ -709,7 +852,7 @@ void configure_kernels() {
     if (device < 16 && done[device]) {
         return;
     }
-    CUDA_CHECK(cudaFuncSetAttribute(backward_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    CUDA_CHECK(cudaFuncSetAttribute(backward_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dqk::SMEM_BYTES));
     CUDA_CHECK(cudaFuncSetAttribute(backward_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     if (device < 16) {
         done[device] = true;
@@ -811,7 +954,7 @@ void mla_prefill_backward_cuda(__nv_bfloat16* dq, __nv_bfloat16* dk_nope, __nv_b
     } else {
         grid = dim3(total_tokens / BIG + batch_size, heads, 1);
     }
-    backward_dq_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(params);
+    backward_dq_kernel<<<grid, THREADS, dqk::SMEM_BYTES, stream>>>(params);
     CUDA_CHECK(cudaGetLastError());
     backward_dkdv_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(params);
     CUDA_CHECK(cudaGetLastError());
