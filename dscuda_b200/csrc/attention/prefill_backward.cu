@@ -125,8 +125,8 @@ __device__ __forceinline__ void init_barriers(BackwardBarriers* bars, uint32_t s
     for (int i = 0; i < 2; ++i) {
         mbar_init(smem_u32(&bars->mma_a[i]), 1);
         mbar_init(smem_u32(&bars->mma_b[i]), 1);
-        mbar_init(smem_u32(&bars->soft_a[i]), BIG);
-        mbar_init(smem_u32(&bars->soft_b[i]), BIG);
+        mbar_init(smem_u32(&bars->soft_a[i]), 2 * BIG);     // every softmax thread works on every tile
+        mbar_init(smem_u32(&bars->soft_b[i]), 2 * BIG);
     }
     mbar_init(smem_u32(&bars->final_full), 1);
     bars->abort_flag = 0;
@@ -705,7 +705,7 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
                 // dV += P^T dO_t
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    mma_ts_elect(tmem_base + TMEM_DV, x_buffer(2 * t) + k * 8, make_smem_desc(do_smem + k * 2048, SUB_CHUNK, 1024), IDESC_DV,
+                    mma_ts_elect(tmem_base + TMEM_DV, x_buffer(2 * t) + (k / 2) * 32 + (k % 2) * 8, make_smem_desc(do_smem + k * 2048, SUB_CHUNK, 1024), IDESC_DV,
                            (t | k) != 0 ? 1U : 0U, leader);
                 }
                 if (t + 1 < tile_count) {
@@ -719,7 +719,7 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
                 // dK += dS^T Q_t
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    mma_ts_elect(tmem_base + TMEM_DK, x_buffer(2 * t + 1) + k * 8, make_smem_desc(q_smem + k * 2048, SUB_CHUNK, 1024), IDESC_DK,
+                    mma_ts_elect(tmem_base + TMEM_DK, x_buffer(2 * t + 1) + (k / 2) * 32 + (k % 2) * 8, make_smem_desc(q_smem + k * 2048, SUB_CHUNK, 1024), IDESC_DK,
                            (t | k) != 0 ? 1U : 0U, leader);
                 }
                 mma_commit_elect(smem_u32(&bars->stage_empty[stage]), leader);
@@ -734,28 +734,31 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
         const uint32_t lane_base = static_cast<uint32_t>((warp % 4) * 32) << 16;
         const int key_pos = key_start + r;
         bool alive = true;
-        for (int t = group; t < tile_count; t += 2) {
+        // Both groups work on every tile: thread = (key row, 32 of the tile's 64 queries), so a
+        // tile's softmax takes half as long and the tensor core rarely waits for it.  Each
+        // thread overwrites only columns it has read itself: queries 32g..32g+31 are fp32
+        // columns 32g..32g+31 and become bf16 columns 32g..32g+15.
+        for (int t = 0; t < tile_count; ++t) {
             const int stage = t % STAGES;
             const uint32_t parity = (t >> 1) & 1;
             alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->stage_full[stage]), (t / STAGES) & 1, abort_flag, &backward_status) &&
-                                                mbar_wait(smem_u32(&bars->mma_a[group]), parity, abort_flag, &backward_status));
+                                                mbar_wait(smem_u32(&bars->mma_a[t & 1]), parity, abort_flag, &backward_status));
             if (!alive) {
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t st_tmem = tmem_base + lane_base + TMEM_X + ((2 * t) % 3) * 64;
-            const uint32_t dpt_tmem = tmem_base + lane_base + TMEM_X + ((2 * t + 1) % 3) * 64;
-            const float2* ld = bars->lse_delta[stage];
-            const int q0 = (first_tile + t) * SUB;
-            const bool masked = q0 < key_start + BIG || q0 + SUB > length;
-            uint32_t sb[SUB];
-            float prob[SUB];
+            const uint32_t st_tmem = tmem_base + lane_base + TMEM_X + ((2 * t) % 3) * 64 + group * 32;
+            const uint32_t dpt_tmem = tmem_base + lane_base + TMEM_X + ((2 * t + 1) % 3) * 64 + group * 32;
+            const float2* ld = bars->lse_delta[stage] + group * 32;
+            const int q0 = (first_tile + t) * SUB + group * 32;
+            const bool masked = q0 < key_start + BIG || q0 + 32 > length;
+            uint32_t sb[32];
+            float prob[32];
             tmem_ld_x32(st_tmem, sb);
-            tmem_ld_x32(st_tmem + 32, sb + 32);
             tmem_wait_ld();
-            uint32_t packed[SUB / 2];
+            uint32_t packed[16];
 #pragma unroll
-            for (int n = 0; n < SUB; ++n) {
+            for (int n = 0; n < 32; ++n) {
                 float value = exp2_approx(fmaf(__uint_as_float(sb[n]), p.scale_log2, -ld[n].x));
                 if (masked) {
                     value = (key_pos <= q0 + n && q0 + n < length) ? value : 0.0F;
@@ -763,32 +766,31 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
                 prob[n] = value;
             }
 #pragma unroll
-            for (int n = 0; n < SUB; n += 2) {
+            for (int n = 0; n < 32; n += 2) {
                 packed[n / 2] = pack_bf16x2(prob[n], prob[n + 1]);
             }
-            tmem_st_x32(st_tmem, packed);
+            tmem_st_x16(st_tmem, packed);
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(smem_u32(&bars->soft_a[group]));
+            mbar_arrive(smem_u32(&bars->soft_a[t & 1]));
 
-            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->mma_b[group]), parity, abort_flag, &backward_status));
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->mma_b[t & 1]), parity, abort_flag, &backward_status));
             if (!alive) {
                 break;
             }
             tc_fence_after_sync();
             tmem_ld_x32(dpt_tmem, sb);
-            tmem_ld_x32(dpt_tmem + 32, sb + 32);
             tmem_wait_ld();
 #pragma unroll
-            for (int n = 0; n < SUB; n += 2) {
+            for (int n = 0; n < 32; n += 2) {
                 const float d0 = prob[n] * (__uint_as_float(sb[n]) - ld[n].y) * p.scale;
                 const float d1 = prob[n + 1] * (__uint_as_float(sb[n + 1]) - ld[n + 1].y) * p.scale;
                 packed[n / 2] = pack_bf16x2(d0, d1);
             }
-            tmem_st_x32(dpt_tmem, packed);
+            tmem_st_x16(dpt_tmem, packed);
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(smem_u32(&bars->soft_b[group]));
+            mbar_arrive(smem_u32(&bars->soft_b[t & 1]));
         }
         if (alive) {
             alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->final_full), 0, abort_flag, &backward_status));
