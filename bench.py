@@ -39,22 +39,11 @@ import torch
 ROOT = pathlib.Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-SCALE = 192 ** -0.5
-FWD_FLOP_PER_PAIR = 2 * (192 + 128)
-BWD_FLOP_PER_PAIR = 2 * (192 + 128 + 128 + 192 + 192)
-WORKLOADS = {
-    "train": dict(batch=2, seq=8192, heads=128, seed=2, dout_std=0.1, backward=True),
-    "prefill": dict(batch=4, seq=4096, heads=128, seed=1, dout_std=1.0, backward=False),
-}
+from dscuda_b200 import workloads
+from dscuda_b200.workloads import BWD_FLOP_PER_PAIR, FWD_FLOP_PER_PAIR, SCALE, causal_pairs
 
-
-def causal_pairs(seq):
-    return seq * (seq + 1) // 2
-
-
-def workload_flops(w):
-    pairs = causal_pairs(w["seq"]) * w["batch"] * w["heads"]
-    return pairs * (FWD_FLOP_PER_PAIR + (BWD_FLOP_PER_PAIR if w["backward"] else 0))
+WORKLOADS = {"train": workloads.CONFIGS["C3"], "prefill": workloads.CONFIGS["C2"]}
+workload_flops = workloads.dense_flops
 
 
 def measured_peaks():
@@ -109,22 +98,6 @@ class ClockSampler:
                     reasons=reasons, samples=len(self.clocks))
 
 
-def device_inputs(w, device):
-    """Seeded N(0,1) bf16 inputs generated on the device (RoPE is input preparation
-    outside the kernels, which take already-rotated q_pe / k_pe)."""
-    g = torch.Generator(device=device).manual_seed(w["seed"])
-    b, s, h = w["batch"], w["seq"], w["heads"]
-
-    def draw(*shape, std=1.0):
-        return (torch.randn(*shape, device=device, generator=g, dtype=torch.float32) * std).bfloat16()
-
-    tensors = dict(q_nope=draw(b, s, h, 128), q_pe=draw(b, s, h, 64), k_nope=draw(b, s, h, 128), k_pe=draw(b, s, 1, 64),
-                   v=draw(b, s, h, 128))
-    if w["backward"]:
-        tensors["dout"] = draw(b, s, h, 128, std=w["dout_std"])
-    return tensors
-
-
 def time_steps(step, steps, warmup, barrier):
     for _ in range(warmup):
         step()
@@ -143,7 +116,7 @@ def time_steps(step, steps, warmup, barrier):
 
 def run_ours(args, rank, world, device):
     from dscuda_b200 import mla
-    from oracle import mla_oracle as oracle  # cpu_baseline leg only
+    from oracle import mla_oracle as oracle  # used by the cpu_baseline leg only
 
     w = dict(WORKLOADS[args.workload])
     for key in ("batch", "seq", "heads"):
@@ -151,13 +124,13 @@ def run_ours(args, rank, world, device):
             w[key] = getattr(args, key)
     peaks = measured_peaks()
     if args.only_decode:
-        decode = bench_decode(mla, oracle, device, peaks, steps=args.steps, warmup=args.warmup, batch=args.decode_batch)
+        decode = bench_decode(mla, device, peaks, steps=args.steps, warmup=args.warmup, batch=args.decode_batch)
         return {"metric": decode["metric"], "value": decode["value"], "unit": decode["unit"], "n_gpus": 1, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": decode["us_per_step"] / 1e3, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": f"decode only: batch {args.decode_batch}, heads 128, lengths uniform in [1024, 32768], seed 3"},
                 "gpu_launches": 2 * args.steps, "roofline": decode["roofline"], "decode": decode} if rank == 0 else None
-    x = device_inputs(w, device)
+    x = workloads.dense_inputs(w, device)
     fwd_in = (x["q_nope"], x["q_pe"], x["k_nope"], x["k_pe"], x["v"])
     out = torch.empty_like(x["v"])
     lse = torch.empty(w["batch"], w["heads"], w["seq"], device=device)
@@ -238,9 +211,10 @@ def run_ours(args, rank, world, device):
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     seconds, e2e_seconds = float(times[0]), float(times[1])
 
-    decode = bench_decode(mla, oracle, device, peaks) if world == 1 and not args.skip_decode else None
+    decode = bench_decode(mla, device, peaks) if world == 1 and not args.skip_decode else None
+    append = bench_cache_append(mla, device, peaks) if world == 1 and not args.skip_decode else None
     cpu = cpu_baseline(oracle, 12.0) if world == 1 and not args.skip_cpu else None
-    varlen = bench_varlen(mla, oracle, device, peaks) if world == 1 and not args.skip_decode else None
+    varlen = bench_varlen(mla, device, peaks) if world == 1 and not args.skip_decode else None
 
     if rank != 0:
         return None
@@ -263,14 +237,14 @@ def run_ours(args, rank, world, device):
                      "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": achieved / peaks["tensor"],
                      "peak_source": peaks["source"] + " sustained cuBLAS bf16", "frac_of_burst_peak": achieved / peaks["tensor_burst"],
                      "traffic": None},
-        "cpu_baseline": cpu, "decode": decode, "varlen": varlen,
+        "cpu_baseline": cpu, "decode": decode, "varlen": varlen, "cache_append": append,
     }
     return line
 
 
-def bench_decode(mla, oracle, device, peaks, steps=20, warmup=3, splits=16, batch=64):
+def bench_decode(mla, device, peaks, steps=20, warmup=3, splits=16, batch=64):
     """Absorbed paged decode at batch 64, heads 128, lengths uniform in [1024, 32768] (seed 3)."""
-    query, cache, table, lengths = oracle.decode_inputs(seed=3, batch=batch, heads=128)
+    query, cache, table, lengths = workloads.decode_inputs(seed=3, batch=batch, heads=128)
     total_tokens = int(lengths.sum())
     q, c, t, n = (z.to(device) for z in (query, cache, table, lengths))
     workspace = mla.decode_workspace(batch, 128, splits, 512, device)
@@ -281,8 +255,8 @@ def bench_decode(mla, oracle, device, peaks, steps=20, warmup=3, splits=16, batc
         mla.mla_decode(q, c, t, n, SCALE, splits=splits, workspace=workspace, output=out, lse=lse)
 
     seconds = time_steps(step, steps, warmup, lambda: None) / steps
-    algorithmic = total_tokens * 576 * 2 + batch * 128 * (576 + 512) * 2 + batch * 128 * 4 + table.numel() * 4 + batch * 4
-    flops = 2 * (576 + 512) * 128 * total_tokens
+    algorithmic = workloads.decode_bytes(lengths, table, batch, 128)
+    flops = workloads.decode_flops(lengths, 128)
     gbs = algorithmic / seconds / 1e9
     return {"metric": "absorbed MLA decode HBM GB/s", "value": gbs, "unit": "GB/s", "us_per_step": seconds * 1e6,
             "tokens": total_tokens, "algorithmic_bytes": algorithmic, "splits": splits, "tflops": flops / seconds / 1e12,
@@ -290,19 +264,14 @@ def bench_decode(mla, oracle, device, peaks, steps=20, warmup=3, splits=16, batc
                          "peak_source": peaks["source"] + " copy bandwidth", "tensor_frac": flops / seconds / 1e12 / peaks["tensor_burst"]}}
 
 
-def bench_varlen(mla, oracle, device, peaks, heads=16, steps=3, warmup=1):
+def bench_varlen(mla, device, peaks, heads=16, steps=3, warmup=1):
     """Packed long-context forward+backward: the 16 sequence lengths of seed 4 (log-uniform in
     [512, 32768], 121 320 tokens), 16 heads per GPU (the per-GPU shard of the 128-head job)."""
-    lengths = oracle.varlen_lengths()
+    lengths = workloads.varlen_lengths()
     total = sum(lengths)
-    g = torch.Generator(device=device).manual_seed(4)
-
-    def draw(*shape, std=1.0):
-        return (torch.randn(*shape, device=device, generator=g, dtype=torch.float32) * std).bfloat16()
-
-    x = (draw(total, heads, 128), draw(total, heads, 64), draw(total, heads, 128), draw(total, 1, 64), draw(total, heads, 128))
-    dout = draw(total, heads, 128, std=0.1)
-    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=device)
+    tensors, cu = workloads.packed_inputs(lengths, heads, 4, device)
+    x = (tensors["q_nope"], tensors["q_pe"], tensors["k_nope"], tensors["k_pe"], tensors["v"])
+    dout = tensors["dout"]
     out = torch.empty_like(x[4])
     lse = torch.empty(heads, total, device=device)
     workspace = mla.prefill_backward_workspace(len(lengths), max(lengths), total, heads, device)
@@ -313,10 +282,30 @@ def bench_varlen(mla, oracle, device, peaks, heads=16, steps=3, warmup=1):
         mla.prefill_backward(dout, out, lse, *x, SCALE, cu, max(lengths), workspace=workspace, grads=grads)
 
     seconds = time_steps(step, steps, warmup, lambda: None) / steps
-    flops = sum(causal_pairs(n) for n in lengths) * heads * (FWD_FLOP_PER_PAIR + BWD_FLOP_PER_PAIR)
-    tflops = flops / seconds / 1e12
+    tflops = workloads.packed_flops(lengths, heads) / seconds / 1e12
     return {"metric": "packed long-context MLA fwd+bwd TFLOP/s per GPU", "value": tflops, "unit": "TFLOP/s", "ms_per_step": seconds * 1e3,
             "tokens": total, "sequences": len(lengths), "heads_per_gpu": heads, "frac_of_measured_sustained_peak": tflops / peaks["tensor"]}
+
+
+def bench_cache_append(mla, device, peaks, batch=64, tokens=4096, steps=20, warmup=3):
+    """Appending `tokens` new rows per sequence to the paged cache (a prefill's worth): 1152 bytes
+    read and 1152 written per token; the rows (302 MB) and the pages they land in exceed the L2."""
+    g = torch.Generator(device=device).manual_seed(5)
+    latent = torch.randn(batch, tokens, 512, device=device, generator=g).bfloat16()
+    rope = torch.randn(batch, tokens, 64, device=device, generator=g).bfloat16()
+    pages = tokens // 64
+    cache = torch.empty(batch * pages, 64, 1, 576, device=device, dtype=torch.bfloat16)
+    table = torch.randperm(batch * pages, device=device, generator=g).to(torch.int32).reshape(batch, pages).contiguous()
+
+    def step():
+        mla.cache_append(cache, latent, rope, table)
+
+    seconds = time_steps(step, steps, warmup, lambda: None) / steps
+    moved = 2 * batch * tokens * 576 * 2
+    gbs = moved / seconds / 1e9
+    return {"metric": "paged cache append HBM GB/s", "value": gbs, "unit": "GB/s", "us_per_step": seconds * 1e6, "tokens": batch * tokens,
+            "algorithmic_bytes": moved, "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
+                                                     "frac": gbs / peaks["hbm"], "peak_source": peaks["source"] + " copy bandwidth"}}
 
 
 def cpu_baseline(oracle, budget_seconds):

@@ -39,7 +39,8 @@ int mla_device_status(bool reset) {
     const int forward = internal::forward_device_status(reset);
     const int absorbed = internal::absorbed_device_status(reset);
     const int backward = internal::backward_device_status(reset);
-    return forward != 0 ? forward : (absorbed != 0 ? absorbed : backward);
+    const int append = internal::append_device_status(reset);
+    return forward != 0 ? forward : (absorbed != 0 ? absorbed : (backward != 0 ? backward : append));
 }
 
 }  // namespace dscuda

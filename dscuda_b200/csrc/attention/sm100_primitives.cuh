@@ -22,6 +22,7 @@ enum DeviceStatus : int {
     STATUS_OK = 0,
     STATUS_WAIT_TIMEOUT = 1,
     STATUS_SMEM_MISALIGNED = 2,    // a kernel that cannot realign found its dynamic shared memory off a 1024-byte boundary
+    STATUS_BAD_INDEX = 3,          // a page number or position outside the cache was skipped
 };
 
 // Roughly 0.1 s at 2 GHz; far above any legitimate wait (microseconds).

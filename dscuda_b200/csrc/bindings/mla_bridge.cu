@@ -77,6 +77,15 @@ extern "C" int dscuda_mla_decode_static(bf16* output, float* lse, const bf16* qu
     });
 }
 
+extern "C" int dscuda_mla_cache_append(bf16* paged_cache, const bf16* latent, const bf16* key_rope, const int* block_table,
+                                       const int* start_positions, const int* token_counts, int batch, int tokens, int rank, int rope,
+                                       int page_size, int pages, int cache_blocks, cudaStream_t stream) {
+    return guarded([&] {
+        dscuda::mla_cache_append_cuda(paged_cache, latent, key_rope, block_table, start_positions, token_counts, batch, tokens, rank, rope,
+                                      page_size, pages, cache_blocks, stream);
+    });
+}
+
 extern "C" int dscuda_mla_prefill_forward(bf16* output, float* lse, const bf16* q_nope, const bf16* q_pe, const bf16* k_nope,
                                           const bf16* k_pe, const bf16* v, const int* cu_seqlens, int batch, int max_sequence,
                                           int total_tokens, int heads, int nope, int rope, int value, float scale,

@@ -92,6 +92,20 @@ def mla_decode(query, paged_cache, block_table, lengths, scale, splits=8, worksp
     return output, lse
 
 
+def cache_append(paged_cache, kv_latent, key_rope, block_table, start_positions=None, token_counts=None):
+    """Writes new tokens into the paged cache in place (`dscuda_mla_cache_append`).
+    paged_cache [blocks,page,1,576], kv_latent [B,T,512], key_rope [B,T,64] bf16, block_table [B,pages] int32;
+    start_positions / token_counts [B] int32 or None (0 / all T rows).  Token t of sequence b lands at
+    position start_positions[b] + t."""
+    _require(paged_cache, kv_latent, key_rope, block_table, start_positions, token_counts)
+    b, t, rank = kv_latent.shape
+    lib = library("mla")
+    checked(lib, "mla", lib.dscuda_mla_cache_append(
+        _ptr(paged_cache), _ptr(kv_latent), _ptr(key_rope), _ptr(block_table), _ptr(start_positions), _ptr(token_counts),
+        b, t, rank, key_rope.shape[-1], paged_cache.shape[1], block_table.shape[1], paged_cache.shape[0], _stream()))
+    return paged_cache
+
+
 def _prefill_dims(q_nope, cu_seqlens, max_seqlen):
     if cu_seqlens is None:
         b, s, h, _ = q_nope.shape

@@ -68,6 +68,16 @@ int dscuda_mla_decode_static(
     int batch, int heads, int rank, int rope, int page_size, int pages, int splits,
     float scale, void* stream);
 
+/* No counterpart in the reference (include/mla.h, mla_cache_append_cuda): writes
+ * the rows [latent | key_rope] of new tokens into the paged cache, in the layout
+ * reference/python/mla.py:11-23 packs on the host.  start_positions and
+ * token_counts may be NULL (0, and all `tokens` rows). */
+int dscuda_mla_cache_append(
+    void* paged_cache, const void* latent, const void* key_rope,
+    const int* block_table, const int* start_positions, const int* token_counts,
+    int batch, int tokens, int rank, int rope, int page_size, int pages, int cache_blocks,
+    void* stream);
+
 /* No counterpart in the reference: non-absorbed causal prefill forward
  * (include/mla.h, mla_prefill_forward_cuda).  cu_seqlens may be NULL (dense). */
 int dscuda_mla_prefill_forward(
@@ -90,7 +100,8 @@ int dscuda_mla_prefill_backward(
     int nope, int rope, int value, float scale, void* stream);
 
 /* No counterpart in the reference: sticky device status of the MLA kernels
- * (0 fine, 1 a bounded in-kernel wait ran out).  Synchronises the device. */
+ * (0 fine, 1 a bounded in-kernel wait ran out, 2 misaligned shared memory, 3 a
+ * cache append skipped an index outside the cache).  Synchronises the device. */
 int dscuda_mla_device_status(int reset);
 
 /* reference: benchmarks/bindings/flash_attention_bridge.cu:13 */

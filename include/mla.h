@@ -207,8 +207,38 @@ void mla_prefill_backward_cuda(
     float scale,
     cudaStream_t stream = nullptr);
 
+// No counterpart in the reference, which packs a whole [B,N,576] tensor into
+// pages on the host (reference/python/mla.py:11-23).  Writes the rows of new
+// tokens into the paged cache that mla_decode_forward_cuda reads: token t of
+// sequence b goes to position start_positions[b] + t (0 when start_positions is
+// null), i.e. page block_table[b][position / page_size], slot position %
+// page_size, and the row is kv_latent[b,t,:] followed by key_rope[b,t,:].
+//   kv_latent [B,T,512], key_rope [B,T,64] bf16; paged_kv_cache
+//   [cache_blocks,page_size,1,576]; block_table [B,pages_per_sequence] int32;
+//   token_counts [B] int32 or null: sequence b appends only its first
+//   token_counts[b] of the T rows (ragged batches).
+// A position past pages_per_sequence * page_size or a page number outside
+// [0, cache_blocks) is not written and sets the device status to 3.
+void mla_cache_append_cuda(
+    __nv_bfloat16* paged_kv_cache,
+    const __nv_bfloat16* kv_latent,
+    const __nv_bfloat16* key_rope,
+    const int* block_table,
+    const int* start_positions,
+    const int* token_counts,
+    int batch_size,
+    int tokens,
+    int kv_rank,
+    int rope_size,
+    int page_size,
+    int pages_per_sequence,
+    int cache_blocks,
+    cudaStream_t stream = nullptr);
+
 // Sticky device status shared by the kernels above: 0 = fine, 1 = a bounded
-// pipeline wait inside a kernel ran out (results of that launch are invalid).
+// pipeline wait inside a kernel ran out (results of that launch are invalid),
+// 2 = a kernel found its shared memory misaligned, 3 = a cache append skipped a
+// page number or position outside the cache.
 // Reading it synchronises the device; it is for tests and diagnosis, not for
 // the hot path.  `reset` clears it after reading.
 int mla_device_status(bool reset);

@@ -86,3 +86,14 @@ def test_host_wrappers_refuse_cpu_tensors():
     x = torch.zeros(1, 4, 2, 128, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="no CPU path"):
         mla.flash_forward(x, x, x, 0.1)
+
+
+def test_cache_append_validates_on_the_host():
+    lib = library.library("mla")
+    args = [None] * 6
+    assert lib.dscuda_mla_cache_append(*args, 1, 4, 256, 64, 64, 2, 8, None) == 1
+    assert b"KV rank 512" in lib.dscuda_mla_last_error()
+    assert lib.dscuda_mla_cache_append(*args, 1, 0, 512, 64, 64, 2, 8, None) == 1
+    assert b"positive batch" in lib.dscuda_mla_last_error()
+    assert lib.dscuda_mla_cache_append(*args, 1, 4, 512, 64, 64, 2, 8, None) == 1
+    assert b"null tensor pointer" in lib.dscuda_mla_last_error()
