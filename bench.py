@@ -213,6 +213,7 @@ def run_ours(args, rank, world, device):
 
     decode = bench_decode(mla, device, peaks) if world == 1 and not args.skip_decode else None
     append = bench_cache_append(mla, device, peaks) if world == 1 and not args.skip_decode else None
+    rope = bench_rope(mla, device, peaks) if world == 1 and not args.skip_decode else None
     cpu = cpu_baseline(oracle, 12.0) if world == 1 and not args.skip_cpu else None
     varlen = bench_varlen(mla, device, peaks) if world == 1 and not args.skip_decode else None
 
@@ -237,7 +238,7 @@ def run_ours(args, rank, world, device):
                      "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": achieved / peaks["tensor"],
                      "peak_source": peaks["source"] + " sustained cuBLAS bf16", "frac_of_burst_peak": achieved / peaks["tensor_burst"],
                      "traffic": None},
-        "cpu_baseline": cpu, "decode": decode, "varlen": varlen, "cache_append": append,
+        "cpu_baseline": cpu, "decode": decode, "varlen": varlen, "cache_append": append, "rope": rope,
     }
     return line
 
@@ -306,6 +307,23 @@ def bench_cache_append(mla, device, peaks, batch=64, tokens=4096, steps=20, warm
     return {"metric": "paged cache append HBM GB/s", "value": gbs, "unit": "GB/s", "us_per_step": seconds * 1e6, "tokens": batch * tokens,
             "algorithmic_bytes": moved, "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
                                                      "frac": gbs / peaks["hbm"], "peak_source": peaks["source"] + " copy bandwidth"}}
+
+
+def bench_rope(mla, device, peaks, batch=2, seq=8192, heads=128, steps=20, warmup=3):
+    """Rotary embedding in place of the training step's q_pe and k_pe (270 MB read and written)."""
+    g = torch.Generator(device=device).manual_seed(6)
+    q_pe = torch.randn(batch, seq, heads, 64, device=device, generator=g).bfloat16()
+    k_pe = torch.randn(batch, seq, 1, 64, device=device, generator=g).bfloat16()
+
+    def step():
+        mla.rope_apply(q_pe, k_pe)
+
+    seconds = time_steps(step, steps, warmup, lambda: None) / steps
+    moved = 2 * (q_pe.numel() + k_pe.numel()) * 2
+    gbs = moved / seconds / 1e9
+    return {"metric": "rotary embedding HBM GB/s", "value": gbs, "unit": "GB/s", "us_per_step": seconds * 1e6, "algorithmic_bytes": moved,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"],
+                         "peak_source": peaks["source"] + " copy bandwidth"}}
 
 
 def cpu_baseline(oracle, budget_seconds):

@@ -86,6 +86,11 @@ extern "C" int dscuda_mla_cache_append(bf16* paged_cache, const bf16* latent, co
     });
 }
 
+extern "C" int dscuda_mla_rope_apply(bf16* q_pe, bf16* k_pe, const int* positions, long long rows, int heads, int sequence_length, int rope,
+                                     float theta, cudaStream_t stream) {
+    return guarded([&] { dscuda::mla_rope_apply_cuda(q_pe, k_pe, positions, rows, heads, sequence_length, rope, theta, stream); });
+}
+
 extern "C" int dscuda_mla_prefill_forward(bf16* output, float* lse, const bf16* q_nope, const bf16* q_pe, const bf16* k_nope,
                                           const bf16* k_pe, const bf16* v, const int* cu_seqlens, int batch, int max_sequence,
                                           int total_tokens, int heads, int nope, int rope, int value, float scale,

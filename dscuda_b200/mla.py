@@ -106,6 +106,24 @@ def cache_append(paged_cache, kv_latent, key_rope, block_table, start_positions=
     return paged_cache
 
 
+def rope_apply(q_pe=None, k_pe=None, positions=None, theta=10000.0):
+    """Rotary embedding in place (`dscuda_mla_rope_apply`) of q_pe [..., H, 64] and/or k_pe [..., 1, 64] (bf16).
+    `positions` int32 [rows] on the device, or None for dense [B, S, ...] tensors (position = index along S)."""
+    _require(q_pe, k_pe, positions)
+    anchor = q_pe if q_pe is not None else k_pe
+    if anchor is None:
+        raise ValueError("nothing to rotate")
+    heads = q_pe.shape[-2] if q_pe is not None else 1
+    rows = anchor.numel() // (anchor.shape[-2] * anchor.shape[-1])
+    if positions is None and anchor.dim() != 4:
+        raise ValueError("packed tensors need explicit positions")
+    sequence = anchor.shape[1] if positions is None else 0
+    lib = library("mla")
+    checked(lib, "mla", lib.dscuda_mla_rope_apply(_ptr(q_pe), _ptr(k_pe), _ptr(positions), rows, heads, sequence, anchor.shape[-1], theta,
+                                                   _stream()))
+    return q_pe, k_pe
+
+
 def _prefill_dims(q_nope, cu_seqlens, max_seqlen):
     if cu_seqlens is None:
         b, s, h, _ = q_nope.shape

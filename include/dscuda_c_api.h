@@ -78,6 +78,13 @@ int dscuda_mla_cache_append(
     int batch, int tokens, int rank, int rope, int page_size, int pages, int cache_blocks,
     void* stream);
 
+/* No counterpart in the reference (include/mla.h, mla_rope_apply_cuda): rotary
+ * embedding in place of q_pe [rows,heads,64] and k_pe [rows,1,64]; either pointer
+ * may be NULL; positions may be NULL (position = row % sequence_length). */
+int dscuda_mla_rope_apply(
+    void* q_pe, void* k_pe, const int* positions,
+    long long rows, int heads, int sequence_length, int rope, float theta, void* stream);
+
 /* No counterpart in the reference: non-absorbed causal prefill forward
  * (include/mla.h, mla_prefill_forward_cuda).  cu_seqlens may be NULL (dense). */
 int dscuda_mla_prefill_forward(

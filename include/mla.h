@@ -235,6 +235,23 @@ void mla_cache_append_cuda(
     int cache_blocks,
     cudaStream_t stream = nullptr);
 
+// No counterpart in the reference, whose benchmarks draw already-rotated inputs.
+// Rotary position embedding, in place, of the 64 rotary columns the attention
+// entry points take: q_pe [rows, heads, 64] and k_pe [rows, 1, 64] (either may be
+// null).  Rotate-half pairing (element i with i + 32), angle = position *
+// theta^(-2i/64).  positions [rows] int32 gives each row's position; when it is
+// null the position is row % sequence_length (dense [B, S] rows).
+void mla_rope_apply_cuda(
+    __nv_bfloat16* q_pe,
+    __nv_bfloat16* k_pe,
+    const int* positions,
+    long long rows,
+    int heads,
+    int sequence_length,
+    int rope_size,
+    float theta,
+    cudaStream_t stream = nullptr);
+
 // Sticky device status shared by the kernels above: 0 = fine, 1 = a bounded
 // pipeline wait inside a kernel ran out (results of that launch are invalid),
 // 2 = a kernel found its shared memory misaligned, 3 = a cache append skipped a

@@ -97,3 +97,13 @@ def test_cache_append_validates_on_the_host():
     assert b"positive batch" in lib.dscuda_mla_last_error()
     assert lib.dscuda_mla_cache_append(*args, 1, 4, 512, 64, 64, 2, 8, None) == 1
     assert b"null tensor pointer" in lib.dscuda_mla_last_error()
+
+
+def test_rope_validates_on_the_host():
+    lib = library.library("mla")
+    assert lib.dscuda_mla_rope_apply(None, None, None, 4, 2, 4, 32, 10000.0, None) == 1
+    assert b"RoPE size 64" in lib.dscuda_mla_last_error()
+    assert lib.dscuda_mla_rope_apply(None, None, None, 4, 2, 0, 64, 10000.0, None) == 1
+    assert b"positions" in lib.dscuda_mla_last_error()
+    assert lib.dscuda_mla_rope_apply(None, None, None, 4, 2, 4, 64, 10000.0, None) == 1
+    assert b"null tensor pointer" in lib.dscuda_mla_last_error()
