@@ -145,26 +145,35 @@ __device__ __forceinline__ void store_bf16_row(__nv_bfloat16* dst, const uint32_
 }
 
 // ---------------------------------------------------------------------------
-// delta[q] = sum_d dO[q,d] * O[q,d]; one warp per (row, head).
+// delta[q] = sum_d dO[q,d] * O[q,d]; half a warp per (row, head).
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) delta_kernel(float* delta, const __nv_bfloat16* dout, const __nv_bfloat16* out, const int* cu_seqlens,
                                                     int batch, int max_seq, int total, int heads) {
     const size_t pairs = static_cast<size_t>(total) * heads;
     const size_t warp_stride = static_cast<size_t>(gridDim.x) * (blockDim.x / 32);
     const int lane = threadIdx.x % 32;
-    for (size_t pair = static_cast<size_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32; pair < pairs; pair += warp_stride) {
-        const uint2 a = *reinterpret_cast<const uint2*>(dout + pair * 128 + lane * 4);
-        const uint2 b = *reinterpret_cast<const uint2*>(out + pair * 128 + lane * 4);
-        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
-        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
-        const float2 a0 = __bfloat1622float2(a2[0]), a1 = __bfloat1622float2(a2[1]);
-        const float2 b0 = __bfloat1622float2(b2[0]), b1 = __bfloat1622float2(b2[1]);
-        float sum = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+    // half a warp per (row, head): 16 lanes x 16 bytes cover the 128 values of dO and of O
+    const int half = lane / 16;
+    const int part = lane % 16;
+    for (size_t base = (static_cast<size_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32) * 2; base < pairs; base += warp_stride * 2) {
+        const size_t pair = base + half;
+        float sum = 0.0F;
+        if (pair < pairs) {
+            const uint4 a = __ldg(reinterpret_cast<const uint4*>(dout + pair * 128) + part);
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(out + pair * 128) + part);
+            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
 #pragma unroll
-        for (int offset = 16; offset > 0; offset >>= 1) {
+            for (int e = 0; e < 4; ++e) {
+                const float2 x = __bfloat1622float2(a2[e]), y = __bfloat1622float2(b2[e]);
+                sum += x.x * y.x + x.y * y.y;
+            }
+        }
+#pragma unroll
+        for (int offset = 8; offset > 0; offset >>= 1) {
             sum += __shfl_xor_sync(0xffffffffU, sum, offset);
         }
-        if (lane == 0) {
+        if (part == 0 && pair < pairs) {
             const size_t row = pair / heads;
             const int head = static_cast<int>(pair % heads);
             size_t index;
