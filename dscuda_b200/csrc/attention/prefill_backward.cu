@@ -27,6 +27,7 @@
 #include "sm100_primitives.cuh"
 #include "../common/tensor_map.h"
 
+#include <cstddef>
 #include <stdexcept>
 
 namespace dscuda {
@@ -81,9 +82,12 @@ struct BackwardBarriers {
     uint64_t final_full;
     uint32_t tmem_base;
     int abort_flag;
-    float2 lse_delta[STAGES][SUB];   // dK/dV kernel: (LSE * log2 e, delta) of the streamed queries
+    alignas(16) float lse2[STAGES][SUB];     // dK/dV kernel: LSE * log2 e of the streamed queries, read 16 bytes at a time
+    alignas(16) float delta[STAGES][SUB];
 };
 static_assert(sizeof(BackwardBarriers) <= MISC_BYTES, "barrier block too large");
+static_assert(offsetof(BackwardBarriers, lse2) % 16 == 0 && offsetof(BackwardBarriers, delta) % 16 == 0 && (SUB * sizeof(float)) % 16 == 0,
+              "16-byte loads of the per-query constants");
 
 // Maps a linear block index to (sequence, block inside the sequence).  Dense:
 // blockIdx.z is the batch entry.  Packed: walk cu_seqlens.  Returns false when
@@ -636,12 +640,13 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
             for (int e = 0; e < SUB / 32; ++e) {
                 const int n = e * 32 + lane;
                 const int q_pos = q0 + n;
-                float2 value = make_float2(0.0F, 0.0F);
+                float lse_value = 0.0F, delta_value = 0.0F;
                 if (q_pos < length) {
-                    value.x = p.lse[lse_offset + q_pos] * LOG2E;
-                    value.y = p.delta[lse_offset + q_pos];
+                    lse_value = p.lse[lse_offset + q_pos] * LOG2E;
+                    delta_value = p.delta[lse_offset + q_pos];
                 }
-                bars->lse_delta[stage][n] = value;
+                bars->lse2[stage][n] = lse_value;
+                bars->delta[stage][n] = delta_value;
             }
             __syncwarp();
             if (lane == 0) {
@@ -758,7 +763,9 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
             tc_fence_after_sync();
             const uint32_t st_tmem = tmem_base + lane_base + TMEM_X + ((2 * t) % 3) * 64 + group * 32;
             const uint32_t dpt_tmem = tmem_base + lane_base + TMEM_X + ((2 * t + 1) % 3) * 64 + group * 32;
-            const float2* ld = bars->lse_delta[stage] + group * 32;
+            // the per-query constants are the same for every lane: 16-byte broadcast loads
+            const float4* lse4 = reinterpret_cast<const float4*>(bars->lse2[stage] + group * 32);
+            const float4* delta4 = reinterpret_cast<const float4*>(bars->delta[stage] + group * 32);
             const int q0 = (first_tile + t) * SUB + group * 32;
             const bool masked = q0 < key_start + BIG || q0 + 32 > length;
             uint32_t sb[32];
@@ -767,12 +774,18 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
             tmem_wait_ld();
             uint32_t packed[16];
 #pragma unroll
-            for (int n = 0; n < 32; ++n) {
-                float value = exp2_approx(fmaf(__uint_as_float(sb[n]), p.scale_log2, -ld[n].x));
-                if (masked) {
-                    value = (key_pos <= q0 + n && q0 + n < length) ? value : 0.0F;
+            for (int n = 0; n < 32; n += 4) {
+                const float4 l = lse4[n / 4];
+                prob[n] = exp2_approx(fmaf(__uint_as_float(sb[n]), p.scale_log2, -l.x));
+                prob[n + 1] = exp2_approx(fmaf(__uint_as_float(sb[n + 1]), p.scale_log2, -l.y));
+                prob[n + 2] = exp2_approx(fmaf(__uint_as_float(sb[n + 2]), p.scale_log2, -l.z));
+                prob[n + 3] = exp2_approx(fmaf(__uint_as_float(sb[n + 3]), p.scale_log2, -l.w));
+            }
+            if (masked) {
+#pragma unroll
+                for (int n = 0; n < 32; ++n) {
+                    prob[n] = (key_pos <= q0 + n && q0 + n < length) ? prob[n] : 0.0F;
                 }
-                prob[n] = value;
             }
 #pragma unroll
             for (int n = 0; n < 32; n += 2) {
@@ -791,10 +804,11 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
             tmem_ld_x32(dpt_tmem, sb);
             tmem_wait_ld();
 #pragma unroll
-            for (int n = 0; n < 32; n += 2) {
-                const float d0 = prob[n] * (__uint_as_float(sb[n]) - ld[n].y) * p.scale;
-                const float d1 = prob[n + 1] * (__uint_as_float(sb[n + 1]) - ld[n + 1].y) * p.scale;
-                packed[n / 2] = pack_bf16x2(d0, d1);
+            for (int n = 0; n < 32; n += 4) {
+                const float4 d = delta4[n / 4];
+                packed[n / 2] = pack_bf16x2(prob[n] * (__uint_as_float(sb[n]) - d.x) * p.scale, prob[n + 1] * (__uint_as_float(sb[n + 1]) - d.y) * p.scale);
+                packed[n / 2 + 1] =
+                    pack_bf16x2(prob[n + 2] * (__uint_as_float(sb[n + 2]) - d.z) * p.scale, prob[n + 3] * (__uint_as_float(sb[n + 3]) - d.w) * p.scale);
             }
             tmem_st_x16(dpt_tmem, packed);
             tmem_wait_st();
