@@ -632,12 +632,19 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                     }
                     fence_proxy_async_smem();
                 }
-                float mx0 = __uint_as_float(sb[0]), mx1 = __uint_as_float(sb[1]);
+                // three-input maxima, four independent chains
+                float mx0 = __uint_as_float(sb[0]), mx1 = __uint_as_float(sb[1]), mx2 = __uint_as_float(sb[2]), mx3 = __uint_as_float(sb[3]);
 #pragma unroll
-                for (int n = 2; n < KEYS; n += 2) {
-                    mx0 = fmaxf(mx0, __uint_as_float(sb[n]));
-                    mx1 = fmaxf(mx1, __uint_as_float(sb[n + 1]));
+                for (int n = 4; n + 7 < KEYS; n += 8) {
+                    mx0 = max3(mx0, __uint_as_float(sb[n]), __uint_as_float(sb[n + 1]));
+                    mx1 = max3(mx1, __uint_as_float(sb[n + 2]), __uint_as_float(sb[n + 3]));
+                    mx2 = max3(mx2, __uint_as_float(sb[n + 4]), __uint_as_float(sb[n + 5]));
+                    mx3 = max3(mx3, __uint_as_float(sb[n + 6]), __uint_as_float(sb[n + 7]));
                 }
+                mx0 = max3(mx0, __uint_as_float(sb[KEYS - 4]), __uint_as_float(sb[KEYS - 3]));
+                mx1 = max3(mx1, __uint_as_float(sb[KEYS - 2]), __uint_as_float(sb[KEYS - 1]));
+                mx0 = fmaxf(mx0, mx2);
+                mx1 = fmaxf(mx1, mx3);
                 const float tile_max = fmaxf(mx0, mx1);
                 if (j == 0) {
                     m_ref = tile_max;
@@ -666,20 +673,23 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                     }
                 }
                 const float bias = -m_ref * p.scale_log2;
-                float sum0 = 0.0F, sum1 = 0.0F;
+                // packed fp32 pairs: one FMA and one add per two scores
+                float2 sums = make_float2(0.0F, 0.0F);
+                const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+                const float2 bias2 = make_float2(bias, bias);
 #pragma unroll
                 for (int c = 0; c < KEYS / 32; ++c) {
                     uint32_t packed[16];
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
-                        const float p0 = exp2_approx(fmaf(__uint_as_float(sb[c * 32 + 2 * e]), p.scale_log2, bias));
-                        const float p1 = exp2_approx(fmaf(__uint_as_float(sb[c * 32 + 2 * e + 1]), p.scale_log2, bias));
-                        sum0 += p0;
-                        sum1 += p1;
-                        packed[e] = pack_bf16x2(p0, p1);
+                        const float2 x = fma2(make_float2(__uint_as_float(sb[c * 32 + 2 * e]), __uint_as_float(sb[c * 32 + 2 * e + 1])), scale2, bias2);
+                        const float2 pr = make_float2(exp2_approx(x.x), exp2_approx(x.y));
+                        sums = add2(sums, pr);
+                        packed[e] = pack_bf16x2(pr.x, pr.y);
                     }
                     tmem_st_x16(s_tmem + c * 16, packed);
                 }
+                const float sum0 = sums.x, sum1 = sums.y;
                 l_sum += sum0 + sum1;
                 if (r == 0) STAMP(0, tile, 3);
                 tmem_wait_st();

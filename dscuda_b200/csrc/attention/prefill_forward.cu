@@ -393,14 +393,17 @@ __global__ void __launch_bounds__(FORWARD_THREADS, 1) attention_forward_kernel(c
                     sb[n] = n <= r ? sb[n] : 0xff800000U;
                 }
             }
+            // three-input maxima: 64 instructions for 128 scores, four independent chains
             float mx0 = __uint_as_float(sb[0]), mx1 = __uint_as_float(sb[1]), mx2 = __uint_as_float(sb[2]), mx3 = __uint_as_float(sb[3]);
 #pragma unroll
-            for (int n = 4; n < TILE_N; n += 4) {
-                mx0 = fmaxf(mx0, __uint_as_float(sb[n]));
-                mx1 = fmaxf(mx1, __uint_as_float(sb[n + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(sb[n + 2]));
-                mx3 = fmaxf(mx3, __uint_as_float(sb[n + 3]));
+            for (int n = 4; n + 7 < TILE_N; n += 8) {
+                mx0 = max3(mx0, __uint_as_float(sb[n]), __uint_as_float(sb[n + 1]));
+                mx1 = max3(mx1, __uint_as_float(sb[n + 2]), __uint_as_float(sb[n + 3]));
+                mx2 = max3(mx2, __uint_as_float(sb[n + 4]), __uint_as_float(sb[n + 5]));
+                mx3 = max3(mx3, __uint_as_float(sb[n + 6]), __uint_as_float(sb[n + 7]));
             }
+            mx0 = max3(mx0, __uint_as_float(sb[TILE_N - 4]), __uint_as_float(sb[TILE_N - 3]));
+            mx1 = max3(mx1, __uint_as_float(sb[TILE_N - 2]), __uint_as_float(sb[TILE_N - 1]));
             const float tile_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             if (j == 0) {
                 m_ref = tile_max;
@@ -428,20 +431,23 @@ __global__ void __launch_bounds__(FORWARD_THREADS, 1) attention_forward_kernel(c
                 }
             }
             const float bias = -m_ref * p.scale_log2;
-            float sum0 = 0.0F, sum1 = 0.0F;
+            // packed fp32 pairs: one FMA and one add per two scores
+            float2 sums = make_float2(0.0F, 0.0F);
+            const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+            const float2 bias2 = make_float2(bias, bias);
 #pragma unroll
             for (int c = 0; c < TILE_N / 32; ++c) {
                 uint32_t packed[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
-                    const float p0 = exp2_approx(fmaf(__uint_as_float(sb[c * 32 + 2 * e]), p.scale_log2, bias));
-                    const float p1 = exp2_approx(fmaf(__uint_as_float(sb[c * 32 + 2 * e + 1]), p.scale_log2, bias));
-                    sum0 += p0;
-                    sum1 += p1;
-                    packed[e] = pack_bf16x2(p0, p1);
+                    const float2 x = fma2(make_float2(__uint_as_float(sb[c * 32 + 2 * e]), __uint_as_float(sb[c * 32 + 2 * e + 1])), scale2, bias2);
+                    const float2 pr = make_float2(exp2_approx(x.x), exp2_approx(x.y));
+                    sums = add2(sums, pr);
+                    packed[e] = pack_bf16x2(pr.x, pr.y);
                 }
                 tmem_st_x16(s_tmem + c * 16, packed);      // P aliases the first 64 columns of S
             }
+            const float sum0 = sums.x, sum1 = sums.y;
             l_sum += sum0 + sum1;
             tmem_wait_st();
             tc_fence_before_sync();
