@@ -14,16 +14,17 @@
 //
 // A 128x512 fp32 output tile would fill all of tensor memory, so a tile is
 // handled by two CTAs: both compute S = Q K^T (K = 576) and each accumulates
-// one 256-column half of O = P V.  Tensor memory per CTA: O 256 columns, S 64
-// columns (P overwrites it in place as bf16), and 192 columns that hold the
-// first 384 columns of Q as an MMA A operand.  That leaves shared memory for
-// the other 192 Q columns (48 KB) and two rings of key chunks: the five 8 KB
-// chunks of a tile that only S needs (ring of 2 tiles) and the four that are
-// also this CTA's V (ring of 3 tiles).  The first ring is released as soon as
-// S is computed, the second after P V, so loads run two to three tiles ahead.
+// one 256-column half of O = P V.  Tensor memory per CTA: O 256 columns, two S
+// buffers of 64 columns (P overwrites S in place as bf16), and 128 columns that
+// hold the four 64-column chunks of Q facing this CTA's V chunks, as an MMA A
+// operand.  Shared memory holds the other five Q chunks (80 KB) and two rings of
+// key chunks, two tiles deep each: the five 8 KB chunks of a tile that only S
+// needs, released as soon as S is computed, and the four that are also this
+// CTA's V, released after P V.
 //
-// Warps 0-3: softmax / epilogue (one thread per row); warp 4: MMA issue;
-// warp 5: TMA loads.  All waits are bounded.
+// Warps 0-3: softmax / epilogue (one thread per row); warp 4: MMA issue (the
+// whole warp runs the loop, one elected lane executes the instruction); warp 5:
+// TMA loads.  All waits are bounded.
 #include "mla.h"
 #include "cuda_common.h"
 #include "attention_internal.h"

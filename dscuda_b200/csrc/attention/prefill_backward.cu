@@ -3,9 +3,10 @@
 // One call launches, on the caller's stream:
 //   1. a memset of the fp32 dk_pe accumulator (first total*64 floats of the workspace);
 //   2. delta_kernel:        delta[q] = sum_d dO[q,d] * O[q,d]            (fp32, LSE layout);
-//   3. backward_dq_kernel:  per 128-row query tile, over 64-key tiles
-//                           S = Q K^T, dP = dO V^T (tcgen05, fp32 in tensor memory),
-//                           P = exp(S*scale - LSE), dS = P (dP - delta) scale (registers),
+//   3. backward_dq_kernel:  per 128-row query tile, over 128-key tiles
+//                           S = Q K^T, dP = dO V^T (tcgen05, fp32 in tensor memory, dO as a
+//                           tensor-memory operand), P = exp(S*scale - LSE),
+//                           dS = P (dP - delta) scale (registers, in two stages),
 //                           dQ += dS K with dS fed from tensor memory;
 //   4. backward_dkdv_kernel: per 128-key tile, over 64-query tiles
 //                           S^T = K Q^T, dP^T = V dO^T, P^T, dS^T as above (one thread per key),
@@ -18,9 +19,9 @@
 // memory columns of one SM together, and splitting keeps every gradient a plain
 // single-writer store (only dk_pe, which sums over heads, uses atomics).
 //
-// Both main kernels: warps 0-3 and 4-7 are two softmax groups that take
-// alternate tiles, warp 8 issues the MMAs from one thread, warp 9 loads with
-// TMA.  Every wait is bounded.
+// Both main kernels: warps 0-7 are the softmax threads (all 256 on the same tile,
+// two per row), warp 8 issues the MMAs (the whole warp runs the loop, one elected
+// lane executes the instruction), warp 9 loads with TMA.  Every wait is bounded.
 #include "mla.h"
 #include "cuda_common.h"
 #include "attention_internal.h"

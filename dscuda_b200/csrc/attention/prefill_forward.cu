@@ -13,9 +13,11 @@
 // shared-memory chunks filled by TMA (one plain load per CTA; K/V reuse between
 // CTAs is served by L2).
 //
-// Warp roles (320 threads): warps 0-3 softmax/epilogue of tile 0, warps 4-7 of
-// tile 1, warp 8 issues every MMA from one thread, warp 9 issues every TMA load
-// from one thread.  All waits are bounded; a wait that runs out raises the
+// Warp roles (384 threads): warps 0-3 softmax/epilogue of tile 0, warps 4-7 of
+// tile 1, warp 8 issues every MMA (the whole warp runs the loop, one elected
+// lane executes the instruction), warp 9 issues every TMA load from one thread,
+// warps 10-11 only complete the third warpgroup so that it can hand registers
+// to the softmax warps.  All waits are bounded; a wait that runs out raises the
 // device status word and the CTA tears down normally (tensor memory freed).
 #include "mla.h"
 #include "flash_attention.h"
