@@ -214,6 +214,7 @@ def run_ours(args, rank, world, device):
     decode = bench_decode(mla, device, peaks) if world == 1 and not args.skip_decode else None
     append = bench_cache_append(mla, device, peaks) if world == 1 and not args.skip_decode else None
     rope = bench_rope(mla, device, peaks) if world == 1 and not args.skip_decode else None
+    absorbed = bench_absorbed(mla, device, peaks) if world == 1 and not args.skip_decode else None
     cpu = cpu_baseline(oracle, 12.0) if world == 1 and not args.skip_cpu else None
     varlen = bench_varlen(mla, device, peaks) if world == 1 and not args.skip_decode else None
 
@@ -238,7 +239,7 @@ def run_ours(args, rank, world, device):
                      "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": achieved / peaks["tensor"],
                      "peak_source": peaks["source"] + " sustained cuBLAS bf16", "frac_of_burst_peak": achieved / peaks["tensor_burst"],
                      "traffic": None},
-        "cpu_baseline": cpu, "decode": decode, "varlen": varlen, "cache_append": append, "rope": rope,
+        "cpu_baseline": cpu, "decode": decode, "varlen": varlen, "cache_append": append, "rope": rope, "absorbed": absorbed,
     }
     return line
 
@@ -307,6 +308,30 @@ def bench_cache_append(mla, device, peaks, batch=64, tokens=4096, steps=20, warm
     return {"metric": "paged cache append HBM GB/s", "value": gbs, "unit": "GB/s", "us_per_step": seconds * 1e6, "tokens": batch * tokens,
             "algorithmic_bytes": moved, "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
                                                      "frac": gbs / peaks["hbm"], "peak_source": peaks["source"] + " copy bandwidth"}}
+
+
+def bench_absorbed(mla, device, peaks, shapes=((1, 512, 8), (4, 2048, 16)), steps=10, warmup=3):
+    """Absorbed causal forward and backward (the reference's four-argument-pair API): its own largest
+    prefill shape (B=1, T=512, H=8) and a larger one.  FLOPs per causal (query, key) pair and head:
+    forward 2*(576+512), backward 2*(576+512+576+576+512)."""
+    rows = []
+    for b, t, h in shapes:
+        g = torch.Generator(device=device).manual_seed(7)
+
+        def draw(*shape):
+            return (torch.randn(*shape, device=device, generator=g) * 0.25).bfloat16()
+
+        q, qr, kv, kr = draw(b, t, h, 512), draw(b, t, h, 64), draw(b, t, 512), draw(b, t, 64)
+        scale = 576 ** -0.5
+        out, lse = mla.mla_forward(q, qr, kv, kr, scale)
+        dout = draw(b, t, h, 512)
+        fwd = time_steps(lambda: mla.mla_forward(q, qr, kv, kr, scale), steps, warmup, lambda: None) / steps
+        bwd = time_steps(lambda: mla.mla_backward(dout, out, lse, q, qr, kv, kr, scale), steps, warmup, lambda: None) / steps
+        pairs = causal_pairs(t) * b * h
+        rows.append({"shape": f"B={b} T={t} H={h}", "forward_us": fwd * 1e6, "backward_us": bwd * 1e6,
+                     "forward_tflops": pairs * 2 * (576 + 512) / fwd / 1e12,
+                     "backward_tflops": pairs * 2 * (576 + 512 + 576 + 576 + 512) / bwd / 1e12})
+    return {"metric": "absorbed MLA causal forward / backward", "kernels": "forward tcgen05; backward CUDA cores", "shapes": rows}
 
 
 def bench_rope(mla, device, peaks, batch=2, seq=8192, heads=128, steps=20, warmup=3):

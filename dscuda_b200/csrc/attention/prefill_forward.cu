@@ -83,6 +83,7 @@ struct ForwardBarriers {
     uint64_t q_full[2];
     uint64_t s_full[2];
     uint64_t p_full[2];
+    uint64_t p_half[2];        // the first 64 keys of P are stored: the first half of P V may start
     uint64_t ring_full[10];
     uint64_t ring_empty[10];
     uint32_t tmem_base;
@@ -156,6 +157,7 @@ __global__ void __launch_bounds__(FORWARD_THREADS, 1) attention_forward_kernel(c
             mbar_init(smem_u32(&bars->q_full[i]), 1);
             mbar_init(smem_u32(&bars->s_full[i]), 1);
             mbar_init(smem_u32(&bars->p_full[i]), TILE_M);
+            mbar_init(smem_u32(&bars->p_half[i]), TILE_M);
         }
         for (int i = 0; i < L::RING; ++i) {
             mbar_init(smem_u32(&bars->ring_full[i]), 1);
@@ -305,6 +307,11 @@ __global__ void __launch_bounds__(FORWARD_THREADS, 1) attention_forward_kernel(c
                     const uint32_t p_tmem = tmem_base + i * TILE_N;
                     for (int half = 0; half < V_CHUNKS && alive; ++half) {
                         const uint32_t v_chunk = wait_chunk(j * L::PER_TILE + KQ + half);
+                        if (alive) {
+                            // keys 0-63 of P are ready before keys 64-127
+                            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(half == 0 ? &bars->p_half[i] : &bars->p_full[i]), j & 1, abort_flag,
+                                                                      &forward_status));
+                        }
                         if (!alive) {
                             return;
                         }
@@ -337,11 +344,6 @@ __global__ void __launch_bounds__(FORWARD_THREADS, 1) attention_forward_kernel(c
                         if (j >= tiles[i]) {
                             continue;
                         }
-                        alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->p_full[i]), j & 1, abort_flag, &forward_status));
-                        if (!alive) {
-                            break;
-                        }
-                        tc_fence_after_sync();
                         issue_pv(i, j);
                         if (!alive) {
                             break;
@@ -448,6 +450,11 @@ __global__ void __launch_bounds__(FORWARD_THREADS, 1) attention_forward_kernel(c
                     packed[e] = pack_bf16x2(pr.x, pr.y);
                 }
                 tmem_st_x16(s_tmem + c * 16, packed);      // P aliases the first 64 columns of S
+                if (c == 1) {
+                    tmem_wait_st();
+                    tc_fence_before_sync();
+                    mbar_arrive(smem_u32(&bars->p_half[i]));
+                }
             }
             const float sum0 = sums.x, sum1 = sums.y;
             l_sum += sum0 + sum1;

@@ -121,7 +121,9 @@ def prefill_embed_case(mla, name, b, s, h, seed):
 
 
 def main():
-    reference = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path of the reference checkout>")
+    reference = pathlib.Path(sys.argv[1])
     sys.path.insert(0, str(reference))
     from reference.python import mla
     torch.manual_seed(0)
