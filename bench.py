@@ -43,6 +43,12 @@ from dscuda_b200 import workloads
 from dscuda_b200.workloads import BWD_FLOP_PER_PAIR, FWD_FLOP_PER_PAIR, SCALE, causal_pairs
 
 WORKLOADS = {"train": workloads.CONFIGS["C3"], "prefill": workloads.CONFIGS["C2"]}
+# DRAM bytes (read + written) per (token, head) of the dominant call, from an ncu capture at
+# B=1, S=8192, H=32 (dram__bytes_read.sum + dram__bytes_write.sum): forward kernel 288.2 MB,
+# dQ kernel 382.8 MB, dK/dV kernel 414.6 MB over 262144 (token, head) pairs.  Between S=4096 and
+# S=8192 at H=32 the traffic grew 2.08-2.11x for 2x the pairs, i.e. in proportion; the bench line
+# scales these figures to its own number of pairs.
+DRAM_BYTES_PER_TOKEN_HEAD = {"forward": 288.2e6 / 262144, "backward": (382.8e6 + 414.6e6) / 262144}
 workload_flops = workloads.dense_flops
 
 
@@ -238,7 +244,8 @@ def run_ours(args, rank, world, device):
         "roofline": {"bound": "tensor", "kernel": "prefill backward (dQ + dK/dV kernels)" if w["backward"] else "attention_forward_kernel<3>",
                      "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": achieved / peaks["tensor"],
                      "peak_source": peaks["source"] + " sustained cuBLAS bf16", "frac_of_burst_peak": achieved / peaks["tensor_burst"],
-                     "traffic": None},
+                     "traffic": DRAM_BYTES_PER_TOKEN_HEAD["backward" if w["backward"] else "forward"] * w["batch"] * w["seq"] * w["heads"],
+                     "traffic_source": "ncu capture at B=1 S=8192 H=32, scaled by (token, head) pairs"},
         "cpu_baseline": cpu, "decode": decode, "varlen": varlen, "cache_append": append, "rope": rope, "absorbed": absorbed,
     }
     return line
