@@ -221,6 +221,7 @@ def run_ours(args, rank, world, device):
     append = bench_cache_append(mla, device, peaks) if world == 1 and not args.skip_decode else None
     rope = bench_rope(mla, device, peaks) if world == 1 and not args.skip_decode else None
     absorbed = bench_absorbed(mla, device, peaks) if world == 1 and not args.skip_decode else None
+    flash = bench_flash(mla, device, peaks) if world == 1 and not args.skip_decode else None
     cpu = cpu_baseline(oracle, 12.0) if world == 1 and not args.skip_cpu else None
     varlen = bench_varlen(mla, device, peaks) if world == 1 and not args.skip_decode else None
 
@@ -246,7 +247,7 @@ def run_ours(args, rank, world, device):
                      "peak_source": peaks["source"] + " sustained cuBLAS bf16", "frac_of_burst_peak": achieved / peaks["tensor_burst"],
                      "traffic": DRAM_BYTES_PER_TOKEN_HEAD["backward" if w["backward"] else "forward"] * w["batch"] * w["seq"] * w["heads"],
                      "traffic_source": "ncu capture at B=1 S=8192 H=32, scaled by (token, head) pairs"},
-        "cpu_baseline": cpu, "decode": decode, "varlen": varlen, "cache_append": append, "rope": rope, "absorbed": absorbed,
+        "cpu_baseline": cpu, "decode": decode, "varlen": varlen, "cache_append": append, "rope": rope, "absorbed": absorbed, "flash": flash,
     }
     return line
 
@@ -339,6 +340,19 @@ def bench_absorbed(mla, device, peaks, shapes=((1, 512, 8), (4, 2048, 16)), step
                      "forward_tflops": pairs * 2 * (576 + 512) / fwd / 1e12,
                      "backward_tflops": pairs * 2 * (576 + 512 + 576 + 576 + 512) / bwd / 1e12})
     return {"metric": "absorbed MLA causal forward / backward", "kernels": "forward tcgen05; backward CUDA cores", "shapes": rows}
+
+
+def bench_flash(mla, device, peaks, batch=4, seq=4096, q_heads=64, kv_heads=8, steps=10, warmup=3):
+    """Causal D=128 grouped-query forward (the flash_attention.h contract): 4*128 FLOP per causal pair and query head."""
+    g = torch.Generator(device=device).manual_seed(9)
+    q = torch.randn(batch, seq, q_heads, 128, device=device, generator=g).bfloat16()
+    k = torch.randn(batch, seq, kv_heads, 128, device=device, generator=g).bfloat16()
+    v = torch.randn(batch, seq, kv_heads, 128, device=device, generator=g).bfloat16()
+    scale = 128 ** -0.5
+    seconds = time_steps(lambda: mla.flash_forward(q, k, v, scale), steps, warmup, lambda: None) / steps
+    tflops = causal_pairs(seq) * batch * q_heads * 4 * 128 / seconds / 1e12
+    return {"metric": "flash attention forward TFLOP/s (D=128 GQA, causal)", "value": tflops, "unit": "TFLOP/s", "ms_per_step": seconds * 1e3,
+            "shape": f"B={batch} T={seq} Hq={q_heads} Hkv={kv_heads}", "frac_of_measured_sustained_peak": tflops / peaks["tensor"]}
 
 
 def bench_rope(mla, device, peaks, batch=2, seq=8192, heads=128, steps=20, warmup=3):

@@ -38,7 +38,6 @@ constexpr int TILE_N = 128;                 // keys per K/V tile
 constexpr int HEAD_V = 128;                 // value width
 constexpr int CHUNK_BYTES = 16384;          // [128 rows x 64 bf16] or [64 keys x 128 bf16]
 constexpr int V_CHUNKS = TILE_N / 64;       // V tile = 2 chunks of 64 keys
-constexpr int SOFTMAX_THREADS = 256;
 constexpr int FORWARD_THREADS = 384;     // warps 10 and 11 only complete the third warpgroup for setmaxnreg
 constexpr int MMA_WARP = 8;
 constexpr int LOAD_WARP = 9;
