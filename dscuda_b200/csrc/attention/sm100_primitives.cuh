@@ -1,6 +1,6 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) features the attention
-// kernels use: mbarrier with bounded waits, TMA tile loads (never with cluster
-// multicast), tcgen05 tensor-memory allocation, MMA issue, commit, and
+// kernels use: mbarrier with bounded waits, plain TMA tile loads (each CTA loads
+// its own tiles), tcgen05 tensor-memory allocation, MMA issue, commit, and
 // tensor-memory loads/stores, plus the shared-memory / instruction descriptor
 // encoders for bf16 operands in 128-byte-swizzled tiles.
 #pragma once
