@@ -192,16 +192,6 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* r) {
         : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-
 __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t* r) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -225,39 +215,6 @@ __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t* r) {
         : "memory");
 }
 
-// ---------------------------------------------------------------------------
-// tcgen05.mma (bf16 x bf16 -> fp32 in tensor memory), one issuing thread.
-// ---------------------------------------------------------------------------
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}\n"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// D[tmem] (+)= A[tmem] * B[smem]; A is K-major: lane = row, two bf16 per column.
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
-        "}\n"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// Makes `bar` complete one arrival once every MMA this thread has issued so
-// far has finished (implies tcgen05.fence::before_thread_sync).
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
 // Warp-uniform issue: the whole warp runs the issue loop (waits, address arithmetic, loop
 // control) and the lane picked by elect_one() executes the tcgen05 instruction.  Measured on
 // B200: an issue loop inside `if (lane == 0)` delivers a 128x128x16 MMA every 86 cycles with the
@@ -275,6 +232,7 @@ __device__ __forceinline__ uint32_t elect_one() {
     return leader;
 }
 
+// D[tmem] (+)= A[smem] * B[smem], executed by the lane with `leader` != 0.
 __device__ __forceinline__ void mma_ss_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
                                              uint32_t leader) {
     asm volatile(
@@ -288,6 +246,7 @@ __device__ __forceinline__ void mma_ss_elect(uint32_t d_tmem, uint64_t a_desc, u
         : "memory");
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]; A is K-major: lane = row, two bf16 per column.
 __device__ __forceinline__ void mma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
                                              uint32_t leader) {
     asm volatile(
@@ -301,6 +260,8 @@ __device__ __forceinline__ void mma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, u
         : "memory");
 }
 
+// Makes `bar` complete one arrival once every MMA the elected lane has issued so far has
+// finished (implies tcgen05.fence::before_thread_sync).
 __device__ __forceinline__ void mma_commit_elect(uint32_t bar, uint32_t leader) {
     asm volatile(
         "{\n\t"
@@ -357,35 +318,6 @@ __host__ __device__ constexpr uint32_t smem_desc_hi(uint32_t stride_bytes) {
 
 __device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr, uint32_t leading_bytes) {
     return ((smem_addr & 0x3FFFFU) >> 4) | (((leading_bytes >> 4) & 0x3FFFU) << 16);
-}
-
-__device__ __forceinline__ void mma_ss_split(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
-                                             uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        ".reg .b64 da, db;\n\t"
-        "setp.ne.b32 p, %6, 0;\n\t"
-        "mov.b64 da, {%1, %2};\n\t"
-        "mov.b64 db, {%3, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
-        "}\n"
-        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void mma_ts_split(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
-                                             uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        ".reg .b64 db;\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "mov.b64 db, {%2, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
-        "}\n"
-        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-        : "memory");
 }
 
 // Elected-lane forms of the split-descriptor MMAs (see elect_one()).
@@ -468,15 +400,6 @@ __device__ __forceinline__ float exp2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-}
-
-// Byte offset of element (row, col) inside a [rows x 64] bf16 tile stored with
-// the 128-byte swizzle TMA and the MMA descriptors above agree on: the 16-byte
-// unit index within a 128-byte row is XORed with row % 8.  The tile base must
-// be 1024-byte aligned.
-__device__ __forceinline__ uint32_t swizzle128_offset(uint32_t row, uint32_t col) {
-    const uint32_t unit = (col >> 3) ^ (row & 7U);
-    return row * 128U + unit * 16U + (col & 7U) * 2U;
 }
 
 }  // namespace sm100
