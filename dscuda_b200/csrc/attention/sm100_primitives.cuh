@@ -215,6 +215,9 @@ __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t* r) {
         : "memory");
 }
 
+// ---------------------------------------------------------------------------
+// tcgen05 MMA issue
+// ---------------------------------------------------------------------------
 // Warp-uniform issue: the whole warp runs the issue loop (waits, address arithmetic, loop
 // control) and the lane picked by elect_one() executes the tcgen05 instruction.  Measured on
 // B200: an issue loop inside `if (lane == 0)` delivers a 128x128x16 MMA every 86 cycles with the
