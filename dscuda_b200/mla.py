@@ -14,9 +14,9 @@ import torch
 from .library import checked, library  # noqa: F401 (re-exported for callers)
 
 
-# kernels one dscuda_mla_prefill_backward call launches (memset, delta pre-pass,
-# dQ kernel, dK/dV kernel, dk_pe conversion)
-PREFILL_BACKWARD_LAUNCHES = 5
+# kernels of this library one dscuda_mla_prefill_backward call launches (delta pre-pass,
+# dQ kernel, dK/dV kernel, dk_pe conversion); the call also enqueues one memset of the accumulator
+PREFILL_BACKWARD_LAUNCHES = 4
 
 
 def _stream() -> int:
