@@ -252,7 +252,7 @@ def run_ours(args, rank, world, device):
     return line
 
 
-def bench_decode(mla, device, peaks, steps=20, warmup=3, splits=16, batch=64):
+def bench_decode(mla, device, peaks, steps=20, warmup=3, splits=8, batch=64):
     """Absorbed paged decode at batch 64, heads 128, lengths uniform in [1024, 32768] (seed 3)."""
     query, cache, table, lengths = workloads.decode_inputs(seed=3, batch=batch, heads=128)
     total_tokens = int(lengths.sum())

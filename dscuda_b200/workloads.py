@@ -26,7 +26,7 @@ CONFIGS: Dict[str, dict] = {
     "C1": dict(kind="dense", batch=1, seq=256, heads=16, seed=0, dout_std=1.0, backward=True),
     "C2": dict(kind="dense", batch=4, seq=4096, heads=128, seed=1, dout_std=1.0, backward=False),
     "C3": dict(kind="dense", batch=2, seq=8192, heads=128, seed=2, dout_std=0.1, backward=True),
-    "C4": dict(kind="decode", batch=64, heads=128, seed=3, low=1024, high=32768, page=64, splits=16),
+    "C4": dict(kind="decode", batch=64, heads=128, seed=3, low=1024, high=32768, page=64, splits=8),
     "C5": dict(kind="packed", sequences=16, heads=16, seed=4, low=512, high=32768, dout_std=0.1, backward=True),
 }
 
