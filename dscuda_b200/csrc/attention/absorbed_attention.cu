@@ -755,12 +755,11 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                 if (valid && half == 0) {
                     record[0] = m_ref * p.scale;
                     record[1] = l_sum;
-                    if (seg.last_of_unit) {
-                        // partial slots this sequence does not use carry no weight
-                        for (int s = seg.slot + 1; s < p.splits; ++s) {
-                            records[static_cast<size_t>(s) * (RANK + 2)] = -INFINITY;
-                            records[static_cast<size_t>(s) * (RANK + 2) + 1] = 0.0F;
-                        }
+                    if (seg.last_of_unit && seg.slot + 1 < p.splits) {
+                        // a sequence fills slots 0..slot in order; the first unused one ends the list
+                        // for the combine kernel (its row sum is 0)
+                        records[static_cast<size_t>(seg.slot + 1) * (RANK + 2)] = -INFINITY;
+                        records[static_cast<size_t>(seg.slot + 1) * (RANK + 2) + 1] = 0.0F;
                     }
                 }
 #pragma unroll
@@ -806,29 +805,29 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(__nv_bfloat16* outp
                                                              int splits) {
     const int row = blockIdx.y * heads + blockIdx.x;
     const float* records = workspace + static_cast<size_t>(row) * splits * (RANK + 2);
+    // Slots are filled in order from 0; the first one with a zero row sum ends the list.
     float maximum = -INFINITY;
-    for (int s = 0; s < splits; ++s) {
-        const float l = records[static_cast<size_t>(s) * (RANK + 2) + 1];
-        if (l > 0.0F) {
-            maximum = fmaxf(maximum, records[static_cast<size_t>(s) * (RANK + 2)]);
+    int used = 0;
+    for (; used < splits; ++used) {
+        const float l = records[static_cast<size_t>(used) * (RANK + 2) + 1];
+        if (!(l > 0.0F)) {
+            break;
         }
+        maximum = fmaxf(maximum, records[static_cast<size_t>(used) * (RANK + 2)]);
     }
     float normalizer = 0.0F;
     float acc[4] = {0.0F, 0.0F, 0.0F, 0.0F};
     const int column = threadIdx.x * 4;
-    for (int s = 0; s < splits; ++s) {
+    for (int s = 0; s < used; ++s) {
         const float* record = records + static_cast<size_t>(s) * (RANK + 2);
-        const float l = record[1];
-        if (l > 0.0F) {
-            const float weight = __expf(record[0] - maximum);
-            normalizer += weight * l;
-            const float2 lo = *reinterpret_cast<const float2*>(record + 2 + column);
-            const float2 hi = *reinterpret_cast<const float2*>(record + 4 + column);
-            acc[0] += weight * lo.x;
-            acc[1] += weight * lo.y;
-            acc[2] += weight * hi.x;
-            acc[3] += weight * hi.y;
-        }
+        const float weight = __expf(record[0] - maximum);
+        normalizer += weight * record[1];
+        const float2 lo = *reinterpret_cast<const float2*>(record + 2 + column);
+        const float2 hi = *reinterpret_cast<const float2*>(record + 4 + column);
+        acc[0] += weight * lo.x;
+        acc[1] += weight * lo.y;
+        acc[2] += weight * hi.x;
+        acc[3] += weight * hi.y;
     }
     const float inverse = 1.0F / normalizer;
     uint2 packed;
