@@ -18,7 +18,8 @@ import sys
 
 ROOT = pathlib.Path(__file__).resolve().parents[1]
 BUILD = ROOT / "build"
-LIBRARIES = ("libdscuda_mla_bench.so", "libdscuda_flash_attention_bench.so")
+# the two product libraries, then the test-only probe library (tests/csrc)
+LIBRARIES = ("libdscuda_mla_bench.so", "libdscuda_flash_attention_bench.so", "libdscuda_test_probes.so")
 
 
 def _tool(name: str) -> str:

@@ -103,24 +103,10 @@ struct AbsorbedParams {
     int page_size;
     int pages;
     int splits;
+    int cache_blocks;       // decode: physical pages in the cache, or 0 when the caller did not say
     float scale;
     float scale_log2;
-#ifdef DSCUDA_DEBUG_DUMP
-    float* debug;           // [128*64 raw S of the first tile][128*258 unnormalised O half, l, m] of CTA (0,0,0)
-    long long* stamps;      // clock64 samples of CTA 0: [role 0..2][tile][8]
-#endif
 };
-
-#ifdef DSCUDA_DEBUG_DUMP
-#define STAMP(role, iteration, slot)                                                                         \
-    do {                                                                                                     \
-        if (p.stamps != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (iteration) < 64) { \
-            p.stamps[((role) * 64 + (iteration)) * 8 + (slot)] = clock64();                                 \
-        }                                                                                                    \
-    } while (0)
-#else
-#define STAMP(role, iteration, slot) do { } while (0)
-#endif
 
 struct Schedule {
     int chunk;          // 64-key tiles per CTA pair (range scheme)
@@ -173,8 +159,14 @@ struct Walker {
     bool done;
 };
 
+// Cached tokens of sequence `b` the kernel will read: the caller's length, held inside
+// [0, capacity of the sequence's block-table row].
+__device__ __forceinline__ int sequence_length(const AbsorbedParams& p, int b) {
+    return max(0, min(p.lengths[b], p.pages * p.page_size));
+}
+
 __device__ __forceinline__ int unit_tiles(const AbsorbedParams& p, int unit, int head_tiles) {
-    return (p.lengths[unit / head_tiles] + KEYS - 1) / KEYS;
+    return (sequence_length(p, unit / head_tiles) + KEYS - 1) / KEYS;
 }
 
 __device__ __forceinline__ bool next_segment(const AbsorbedParams& p, const Schedule& s, Walker& w, Segment& seg, int pair, int pairs) {
@@ -236,7 +228,7 @@ __device__ __forceinline__ bool next_segment(const AbsorbedParams& p, const Sche
 
 __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __grid_constant__ AbsorbedParams p) {
     extern __shared__ uint8_t smem_raw[];
-    if (*reinterpret_cast<volatile int*>(&absorbed_status) != 0) {
+    if (*reinterpret_cast<volatile int*>(&absorbed_status) == STATUS_WAIT_TIMEOUT) {
         return;
     }
     const int warp = threadIdx.x / 32;
@@ -283,7 +275,7 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
             long long total = 0;
             int longest = 0;
             for (int b = 0; b < p.batch; ++b) {
-                const int tiles = (p.lengths[b] + KEYS - 1) / KEYS;
+                const int tiles = (sequence_length(p, b) + KEYS - 1) / KEYS;
                 total += static_cast<long long>(tiles) * head_tiles;
                 longest = max(longest, tiles);
             }
@@ -388,6 +380,11 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                     table_entry = ahead < seg.tile_end * KEYS
                                       ? __ldg(p.block_table + static_cast<size_t>(seg.b) * p.pages + ahead / p.page_size)
                                       : 0;
+                    if (p.cache_blocks > 0 && static_cast<unsigned>(table_entry) >= static_cast<unsigned>(p.cache_blocks)) {
+                        // a page number outside the cache: read page 0 instead and report it
+                        atomicExch(&absorbed_status, STATUS_BAD_INDEX);
+                        table_entry = 0;
+                    }
                 }
                 const int physical_page = __shfl_sync(0xffffffffU, table_entry, j & 31);
                 if (lane == 0) {
@@ -399,7 +396,6 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                         alive = mbar_wait(smem_u32(&bars->empty_a[slot_a]), (tile / A_SLOTS - 1) & 1, abort_flag, &absorbed_status);
                     }
                     if (alive) {
-                        STAMP(2, tile, 0);
                         const uint32_t bar = smem_u32(&bars->full_a[slot_a]);
                         mbar_arrive_expect_tx(bar, A_UNIT_BYTES);
                         for (int i = 0; i < A_CHUNKS; ++i) {
@@ -421,7 +417,6 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                         alive = mbar_wait(smem_u32(&bars->empty_b[slot_b]), (tile / B_SLOTS - 1) & 1, abort_flag, &absorbed_status);
                     }
                     if (alive) {
-                        STAMP(2, tile, 1);
                         const uint32_t bar = smem_u32(&bars->full_b[slot_b]);
                         mbar_arrive_expect_tx(bar, B_UNIT_BYTES);
                         for (int i = 0; i < B_CHUNKS; ++i) {
@@ -508,13 +503,11 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                             break;
                         }
                     }
-                    STAMP(1, tile, 4);
                     // ---- O (+)= P V ----
                     alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->p_full[tile & 1]), (tile >> 1) & 1, abort_flag, &absorbed_status));
                     if (!alive) {
                         break;
                     }
-                    STAMP(1, tile, 5);
                     tc_fence_after_sync();
                     const uint32_t p_tmem = tmem_base + TMEM_S + (tile & 1) * KEYS;
 #pragma unroll
@@ -523,7 +516,6 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                                      (j | k) != 0 ? 1U : 0U, leader);
                     }
                     mma_commit_elect(smem_u32(&bars->empty_b[slot_b]), leader);
-                    STAMP(1, tile, 6);
                     if (j + 1 < tile_count) {
                         issue_b_part(tile + 1);
                     }
@@ -551,7 +543,7 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
             int limit;           // this row sees keys < limit
             if (decode) {
                 valid_rows = min(ROWS, p.heads - seg.row_tile * ROWS);
-                kv_end = min(p.lengths[seg.b], seg.tile_end * KEYS);
+                kv_end = min(sequence_length(p, seg.b), seg.tile_end * KEYS);
                 min_limit = kv_end;
                 limit = kv_end;
             } else {
@@ -593,25 +585,15 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
             for (int j = 0; j < tile_count && alive; ++j) {
                 const int tile = tile_index + j;
                 const uint32_t s_tmem = tmem_base + lane_base + TMEM_S + (tile & 1) * KEYS;
-                if (r == 0) STAMP(0, tile, 0);
                 alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->s_full[tile & 1]), (tile >> 1) & 1, abort_flag, &absorbed_status));
                 if (!alive) {
                     break;
                 }
-                if (r == 0) STAMP(0, tile, 1);
                 tc_fence_after_sync();
                 uint32_t sb[KEYS];
                 tmem_ld_x32(s_tmem, sb);
                 tmem_ld_x32(s_tmem + 32, sb + 32);
                 tmem_wait_ld();
-                if (r == 0) STAMP(0, tile, 2);
-#ifdef DSCUDA_DEBUG_DUMP
-                if (p.debug != nullptr && j == 0 && segment_index == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-                    for (int n = 0; n < KEYS; ++n) {
-                        p.debug[r * KEYS + n] = __uint_as_float(sb[n]);
-                    }
-                }
-#endif
                 const int token0 = (seg.tile_begin + j) * KEYS;
                 if (token0 + KEYS > min_limit) {
 #pragma unroll
@@ -692,11 +674,9 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                 }
                 const float sum0 = sums.x, sum1 = sums.y;
                 l_sum += sum0 + sum1;
-                if (r == 0) STAMP(0, tile, 3);
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(smem_u32(&bars->p_full[tile & 1]));
-                if (r == 0) STAMP(0, tile, 4);
             }
 
             if (alive) {
@@ -707,21 +687,6 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
             }
             tc_fence_after_sync();
             const bool valid = r < valid_rows;
-#ifdef DSCUDA_DEBUG_DUMP
-            if (p.debug != nullptr && segment_index == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-                float* dump = p.debug + ROWS * KEYS + r * 258;
-                for (int c = 0; c < HALF_V / 32; ++c) {
-                    uint32_t o[32];
-                    tmem_ld_x32(o_tmem + c * 32, o);
-                    tmem_wait_ld();
-                    for (int e = 0; e < 32; ++e) {
-                        dump[c * 32 + e] = __uint_as_float(o[e]);
-                    }
-                }
-                dump[256] = l_sum;
-                dump[257] = m_ref;
-            }
-#endif
             if (!decode) {
                 const int row = seg.row_tile * ROWS + r;                 // (token, head) index inside the sequence
                 const float inverse = 1.0F / l_sum;
@@ -752,9 +717,15 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                 const int head = seg.row_tile * ROWS + (valid ? r : 0);
                 float* records = p.workspace + (static_cast<size_t>(seg.b) * p.heads + head) * p.splits * (RANK + 2);
                 float* record = records + static_cast<size_t>(seg.slot) * (RANK + 2);
+                // Each CTA of the pair normalises its own 256 columns with its own (maximum, sum):
+                // the two keep separate running maxima (their score chunks are summed in
+                // different orders), so only a normalised partial is independent of which
+                // maximum a CTA happened to hold.  The record then carries the partial's
+                // log-sum-exp and a sum of 1.
+                const float inverse = 1.0F / l_sum;
                 if (valid && half == 0) {
-                    record[0] = m_ref * p.scale;
-                    record[1] = l_sum;
+                    record[0] = m_ref * p.scale + logf(l_sum);
+                    record[1] = 1.0F;
                     if (seg.last_of_unit && seg.slot + 1 < p.splits) {
                         // a sequence fills slots 0..slot in order; the first unused one ends the list
                         // for the combine kernel (its row sum is 0)
@@ -771,7 +742,7 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                         float2* dst = reinterpret_cast<float2*>(record + 2 + half * HALF_V + c * 32);
 #pragma unroll
                         for (int e = 0; e < 32; e += 2) {
-                            dst[e / 2] = make_float2(__uint_as_float(o[e]), __uint_as_float(o[e + 1]));
+                            dst[e / 2] = make_float2(__uint_as_float(o[e]) * inverse, __uint_as_float(o[e + 1]) * inverse);
                         }
                     }
                 }
@@ -799,11 +770,22 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
     }
 }
 
-// Merges the split partials of one (sequence, head): weights exp(m_s - max m),
-// normalises, writes bf16 output and the natural-log LSE.
-__global__ void __launch_bounds__(128) decode_combine_kernel(__nv_bfloat16* output, float* logsumexp, const float* workspace, int heads,
-                                                             int splits) {
+// Merges the split partials of one (sequence, head).  A record is (log-sum-exp of the
+// partial, 1, normalised output); the partials are weighted by exp(lse_s - max lse).
+// Writes bf16 output and the natural-log LSE.  A sequence without cached tokens has no
+// partial at all: its output is NaN and its LSE -inf, what the softmax of an empty row
+// gives in the reference (reference/python/mla.py:36-38).
+__global__ void __launch_bounds__(128) decode_combine_kernel(__nv_bfloat16* output, float* logsumexp, const float* workspace,
+                                                             const int* lengths, int heads, int splits) {
     const int row = blockIdx.y * heads + blockIdx.x;
+    if (lengths[blockIdx.y] <= 0) {
+        const uint32_t nan2 = 0x7fc07fc0U;
+        *reinterpret_cast<uint2*>(output + static_cast<size_t>(row) * RANK + threadIdx.x * 4) = make_uint2(nan2, nan2);
+        if (threadIdx.x == 0) {
+            logsumexp[row] = -INFINITY;
+        }
+        return;
+    }
     const float* records = workspace + static_cast<size_t>(row) * splits * (RANK + 2);
     // Slots are filled in order from 0; the first one with a zero row sum ends the list.
     float maximum = -INFINITY;
@@ -889,10 +871,6 @@ void check_aligned(std::initializer_list<const void*> pointers) {
 
 namespace internal {
 
-#ifdef DSCUDA_DEBUG_DUMP
-float* absorbed_debug_buffer = nullptr;
-long long* absorbed_debug_stamps = nullptr;
-#endif
 
 int absorbed_device_status(bool reset) {
     int status = 0;
@@ -940,10 +918,6 @@ void mla_compressed_attention_forward_cuda(__nv_bfloat16* output, float* logsume
     params.page_size = KEYS;
     params.scale = scale;
     params.scale_log2 = scale * 1.4426950408889634F;
-#ifdef DSCUDA_DEBUG_DUMP
-    params.debug = internal::absorbed_debug_buffer;
-    params.stamps = internal::absorbed_debug_stamps;
-#endif
     configure_kernel();
     const dim3 grid(1, static_cast<unsigned>((rows_per_sequence + ROWS - 1) / ROWS * 2), batch_size);
     absorbed_attention_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(params);
@@ -955,9 +929,13 @@ std::size_t mla_decode_workspace_elements(int batch_size, int heads, int splits,
     return static_cast<std::size_t>(batch_size) * heads * splits * (kv_rank + 2);
 }
 
-void mla_decode_forward_cuda(__nv_bfloat16* output, float* logsumexp, const __nv_bfloat16* query, const __nv_bfloat16* paged_kv_cache,
-                             const int* block_table, const int* cache_lengths, float* workspace, int batch_size, int heads, int kv_rank,
-                             int rope_size, int page_size, int pages_per_sequence, int splits, float scale, cudaStream_t stream) {
+namespace {
+
+// Shared by the decode entry points.  `cache_blocks` <= 0: the number of physical pages is
+// unknown (the reference's interface does not carry it).
+void launch_decode(__nv_bfloat16* output, float* logsumexp, const __nv_bfloat16* query, const __nv_bfloat16* paged_kv_cache,
+                   const int* block_table, const int* cache_lengths, float* workspace, int batch_size, int heads, int kv_rank,
+                   int rope_size, int page_size, int pages_per_sequence, int cache_blocks, int splits, float scale, cudaStream_t stream) {
     check_absorbed_shape(kv_rank, rope_size);
     if (batch_size <= 0 || heads <= 0 || pages_per_sequence <= 0 || splits <= 0) {
         throw std::invalid_argument("MLA decode requires positive batch, heads, pages and splits");
@@ -968,7 +946,8 @@ void mla_decode_forward_cuda(__nv_bfloat16* output, float* logsumexp, const __nv
     if (!(scale > 0.0F)) {
         throw std::invalid_argument("MLA decode requires a positive softmax scale");
     }
-    if (batch_size > 65535 || splits > 65535 || static_cast<long long>(batch_size) * heads > 0x7fffffffLL) {
+    if (batch_size > 65535 || splits > 65535 || static_cast<long long>(batch_size) * heads > 0x7fffffffLL ||
+        static_cast<long long>(pages_per_sequence) * page_size > 0x7fffffffLL) {
         throw std::invalid_argument("MLA decode shape exceeds the supported index range");
     }
     check_aligned({output, logsumexp, query, paged_kv_cache, workspace});
@@ -977,10 +956,10 @@ void mla_decode_forward_cuda(__nv_bfloat16* output, float* logsumexp, const __nv
     }
     AbsorbedParams params{};
     const std::uint64_t q_rows = static_cast<std::uint64_t>(batch_size) * heads;
-    // The number of physical pages is not part of the interface; the view is
-    // given the largest row count a tensor map can hold and only rows named by
-    // the block table are ever touched.
-    const std::uint64_t k_rows = 1ULL << 31;
+    // Without a page count the view is given the largest row count a tensor map can hold and
+    // only rows named by the block table are ever touched.  With one, the view ends where the
+    // cache ends and a page number outside it is replaced and reported by the kernel.
+    const std::uint64_t k_rows = cache_blocks > 0 ? static_cast<std::uint64_t>(cache_blocks) * page_size : 1ULL << 31;
     params.q_lat = make_bf16_tile_map(query, q_rows, RANK, WIDTH, ROWS);
     params.q_rope = make_bf16_tile_map(query + RANK, q_rows, ROPE, WIDTH, ROWS);
     params.k_lat = make_bf16_tile_map(paged_kv_cache, k_rows, RANK, WIDTH, KEYS);
@@ -995,20 +974,37 @@ void mla_decode_forward_cuda(__nv_bfloat16* output, float* logsumexp, const __nv
     params.page_size = page_size;
     params.pages = pages_per_sequence;
     params.splits = splits;
+    params.cache_blocks = cache_blocks > 0 ? cache_blocks : 0;
     params.scale = scale;
     params.scale_log2 = scale * 1.4426950408889634F;
-#ifdef DSCUDA_DEBUG_DUMP
-    params.debug = internal::absorbed_debug_buffer;
-    params.stamps = internal::absorbed_debug_stamps;
-#endif
     configure_kernel();
     // one CTA per SM, in pairs that share a key range (the two halves of the value columns)
     const int pairs = std::max(1, multiprocessor_count() / 2);
     const dim3 grid(2 * pairs, 1, 1);
     absorbed_attention_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(params);
     CUDA_CHECK(cudaGetLastError());
-    decode_combine_kernel<<<dim3(heads, batch_size), 128, 0, stream>>>(output, logsumexp, workspace, heads, splits);
+    decode_combine_kernel<<<dim3(heads, batch_size), 128, 0, stream>>>(output, logsumexp, workspace, cache_lengths, heads, splits);
     CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace
+
+void mla_decode_forward_cuda(__nv_bfloat16* output, float* logsumexp, const __nv_bfloat16* query, const __nv_bfloat16* paged_kv_cache,
+                             const int* block_table, const int* cache_lengths, float* workspace, int batch_size, int heads, int kv_rank,
+                             int rope_size, int page_size, int pages_per_sequence, int splits, float scale, cudaStream_t stream) {
+    launch_decode(output, logsumexp, query, paged_kv_cache, block_table, cache_lengths, workspace, batch_size, heads, kv_rank, rope_size,
+                  page_size, pages_per_sequence, 0, splits, scale, stream);
+}
+
+void mla_decode_forward_checked_cuda(__nv_bfloat16* output, float* logsumexp, const __nv_bfloat16* query,
+                                     const __nv_bfloat16* paged_kv_cache, const int* block_table, const int* cache_lengths,
+                                     float* workspace, int batch_size, int heads, int kv_rank, int rope_size, int page_size,
+                                     int pages_per_sequence, int cache_blocks, int splits, float scale, cudaStream_t stream) {
+    if (cache_blocks <= 0) {
+        throw std::invalid_argument("checked MLA decode requires the number of cache pages");
+    }
+    launch_decode(output, logsumexp, query, paged_kv_cache, block_table, cache_lengths, workspace, batch_size, heads, kv_rank, rope_size,
+                  page_size, pages_per_sequence, cache_blocks, splits, scale, stream);
 }
 
 std::size_t mla_decode_static_capacity() {

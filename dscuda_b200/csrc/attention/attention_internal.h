@@ -16,10 +16,9 @@ namespace internal {
 void check_prefill_shape(const int* cu_seqlens, int batch_size, int max_sequence_length, int total_tokens, int heads,
                          int nope_size, int rope_size, int value_size, float scale);
 
-// `debug` is only honoured by diagnostic builds (DSCUDA_DEBUG_DUMP).
 void launch_prefill_forward(__nv_bfloat16* output, float* logsumexp, const __nv_bfloat16* q_nope, const __nv_bfloat16* q_pe,
                             const __nv_bfloat16* k_nope, const __nv_bfloat16* k_pe, const __nv_bfloat16* v, const int* cu_seqlens,
-                            int batch_size, int max_sequence_length, int total_tokens, int heads, float scale, float* debug,
+                            int batch_size, int max_sequence_length, int total_tokens, int heads, float scale,
                             cudaStream_t stream);
 
 // Per-translation-unit sticky status words (0 = fine).  Reading synchronises.

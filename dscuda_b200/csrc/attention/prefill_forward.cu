@@ -63,9 +63,6 @@ struct ForwardParams {
     int group;              // query heads per K/V head
     float scale;            // softmax scale
     float scale_log2;       // scale * log2(e)
-#ifdef DSCUDA_DEBUG_DUMP
-    float* debug;           // [128*128 raw S of tile 0, KV tile 0][128*130 unnormalised O, l, m]
-#endif
 };
 
 template <int KQ>
@@ -187,10 +184,8 @@ __global__ void __launch_bounds__(FORWARD_THREADS, 1) attention_forward_kernel(c
     // score row in registers and spills at 168, so warps 8-11 hand registers to warps 0-7.  The
     // two setmaxnreg instructions sit inside the role branches: after a join of branches with
     // different limits the compiler assumes the lower one for all the code that follows.
-#ifndef REG_LO
-#define REG_LO 88
-#define REG_HI 208
-#endif
+    constexpr int REG_LO = 88;
+    constexpr int REG_HI = 208;
     // The increase blocks until the CTA's pool holds the registers: what warps 8-11 release must
     // cover what warps 0-7 request, or the kernel never starts (launch allocation: 168 each).
     static_assert(8 * (REG_HI - 168) <= 4 * (168 - REG_LO), "register redistribution exceeds the CTA's allocation");
@@ -382,13 +377,6 @@ __global__ void __launch_bounds__(FORWARD_THREADS, 1) attention_forward_kernel(c
                 tmem_ld_x32(s_tmem + c * 32, sb + c * 32);
             }
             tmem_wait_ld();
-#ifdef DSCUDA_DEBUG_DUMP
-            if (p.debug != nullptr && i == 0 && j == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0) {
-                for (int n = 0; n < TILE_N; ++n) {
-                    p.debug[r * TILE_N + n] = __uint_as_float(sb[n]);
-                }
-            }
-#endif
             if (j == count - 1) {
                 // diagonal tile: key n of the tile is allowed for row r iff n <= r
 #pragma unroll
@@ -475,16 +463,6 @@ __global__ void __launch_bounds__(FORWARD_THREADS, 1) attention_forward_kernel(c
                 uint32_t o[32];
                 tmem_ld_x32(o_tmem + c * 32, o);
                 tmem_wait_ld();
-#ifdef DSCUDA_DEBUG_DUMP
-                if (p.debug != nullptr && i == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0) {
-                    float* dump = p.debug + TILE_M * TILE_N + r * 130;
-                    for (int e = 0; e < 32; ++e) {
-                        dump[c * 32 + e] = __uint_as_float(o[e]);
-                    }
-                    dump[128] = l_sum;
-                    dump[129] = m_ref;
-                }
-#endif
                 if (valid) {
 #pragma unroll
                     for (int e = 0; e < 32; e += 8) {
@@ -552,7 +530,7 @@ namespace internal {
 
 void launch_prefill_forward(__nv_bfloat16* output, float* logsumexp, const __nv_bfloat16* q_nope, const __nv_bfloat16* q_pe,
                             const __nv_bfloat16* k_nope, const __nv_bfloat16* k_pe, const __nv_bfloat16* v, const int* cu_seqlens,
-                            int batch_size, int max_sequence_length, int total_tokens, int heads, float scale, float* debug,
+                            int batch_size, int max_sequence_length, int total_tokens, int heads, float scale,
                             cudaStream_t stream) {
     check_pointers({output, logsumexp, q_nope, q_pe, k_nope, k_pe, v});
     ForwardParams params{};
@@ -572,11 +550,6 @@ void launch_prefill_forward(__nv_bfloat16* output, float* logsumexp, const __nv_
     params.group = 1;
     params.scale = scale;
     params.scale_log2 = scale * 1.4426950408889634F;
-#ifdef DSCUDA_DEBUG_DUMP
-    params.debug = debug;
-#else
-    (void)debug;
-#endif
     configure_forward_kernel<3>();
     dim3 grid;
     if (cu_seqlens == nullptr) {
@@ -607,7 +580,7 @@ void mla_prefill_forward_cuda(__nv_bfloat16* output, float* logsumexp, const __n
                               int value_size, float scale, cudaStream_t stream) {
     internal::check_prefill_shape(cu_seqlens, batch_size, max_sequence_length, total_tokens, heads, nope_size, rope_size, value_size, scale);
     internal::launch_prefill_forward(output, logsumexp, q_nope, q_pe, k_nope, k_pe, v, cu_seqlens, batch_size, max_sequence_length,
-                                     total_tokens, heads, scale, nullptr, stream);
+                                     total_tokens, heads, scale, stream);
 }
 
 void flash_attention_forward_cuda(__nv_bfloat16* output, float* logsumexp, const __nv_bfloat16* query, const __nv_bfloat16* key,

@@ -84,11 +84,13 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 
-// Waits for the phase with the given parity to complete.  Gives up when the
-// time limit passes or when another thread of the CTA has already given up
-// (`abort_flag`, in shared memory); then it raises both flags and returns
-// false, and the caller must leave its loop and go to the common teardown.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word) {
+// Waits for the phase with the given parity to complete.  Gives up when
+// `limit_cycles` of clock64 time have passed or when another thread of the CTA
+// has already given up (`abort_flag`, in shared memory); then it raises both
+// flags and returns false, and the caller must leave its loop and go to the
+// common teardown.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word,
+                                                long long limit_cycles) {
     if (mbar_test_wait(bar, parity)) {
         return true;
     }
@@ -101,13 +103,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             return true;
         }
         if ((spin & 31U) == 0U) {
-            if (*abort_flag != 0 || clock64() - start > WAIT_LIMIT_CYCLES) {
+            if (*abort_flag != 0 || clock64() - start > limit_cycles) {
                 *abort_flag = 1;
                 atomicExch(status_word, STATUS_WAIT_TIMEOUT);
                 return false;
             }
         }
     }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word) {
+    return mbar_wait_limit(bar, parity, abort_flag, status_word, WAIT_LIMIT_CYCLES);
 }
 
 // Register re-distribution between warpgroups (all four warps of a warpgroup

@@ -64,6 +64,15 @@ extern "C" int dscuda_mla_decode(bf16* output, float* lse, const bf16* query, co
     });
 }
 
+extern "C" int dscuda_mla_decode_checked(bf16* output, float* lse, const bf16* query, const bf16* paged_cache, const int* block_table,
+                                         const int* lengths, float* workspace, int batch, int heads, int rank, int rope, int page_size,
+                                         int pages, int cache_blocks, int splits, float scale, cudaStream_t stream) {
+    return guarded([&] {
+        dscuda::mla_decode_forward_checked_cuda(output, lse, query, paged_cache, block_table, lengths, workspace, batch, heads, rank,
+                                                rope, page_size, pages, cache_blocks, splits, scale, stream);
+    });
+}
+
 extern "C" std::size_t dscuda_mla_decode_static_capacity() {
     return dscuda::mla_decode_static_capacity();
 }
@@ -124,25 +133,3 @@ extern "C" int dscuda_mla_device_status(int reset) {
     return status;
 }
 
-#ifdef DSCUDA_DEBUG_DUMP
-// Diagnostic builds only: raw score / accumulator dumps of the first CTA.
-#include "../attention/attention_internal.h"
-namespace dscuda { namespace internal { extern float* absorbed_debug_buffer; extern long long* absorbed_debug_stamps; } }
-
-extern "C" void dscuda_debug_set_absorbed_stamps(long long* stamps) {
-    dscuda::internal::absorbed_debug_stamps = stamps;
-}
-
-extern "C" int dscuda_debug_prefill_forward(bf16* output, float* lse, const bf16* q_nope, const bf16* q_pe, const bf16* k_nope,
-                                            const bf16* k_pe, const bf16* v, const int* cu_seqlens, int batch, int max_sequence,
-                                            int total_tokens, int heads, float scale, float* debug, cudaStream_t stream) {
-    return guarded([&] {
-        dscuda::internal::launch_prefill_forward(output, lse, q_nope, q_pe, k_nope, k_pe, v, cu_seqlens, batch, max_sequence,
-                                                 total_tokens, heads, scale, debug, stream);
-    });
-}
-
-extern "C" void dscuda_debug_set_absorbed_buffer(float* debug) {
-    dscuda::internal::absorbed_debug_buffer = debug;
-}
-#endif

@@ -22,6 +22,7 @@ MLA_SYMBOLS = {
     "dscuda_mla_backward": ([P] * 11 + [I] * 5 + [F, P], I),
     "dscuda_mla_workspace_elements": ([I] * 4, ctypes.c_size_t),
     "dscuda_mla_decode": ([P] * 7 + [I] * 7 + [F, P], I),
+    "dscuda_mla_decode_checked": ([P] * 7 + [I] * 8 + [F, P], I),
     "dscuda_mla_decode_static_capacity": ([], ctypes.c_size_t),
     "dscuda_mla_decode_static": ([P] * 6 + [I] * 7 + [F, P], I),
     "dscuda_mla_cache_append": ([P] * 6 + [I] * 7 + [P], I),

@@ -71,8 +71,9 @@ def decode_workspace(batch, heads, splits, rank=512, device="cuda"):
     return torch.empty(lib.dscuda_mla_workspace_elements(batch, heads, splits, rank), device=device, dtype=torch.float32)
 
 
-def mla_decode(query, paged_cache, block_table, lengths, scale, splits=8, workspace=None, output=None, lse=None):
-    """Paged decode (`dscuda_mla_decode`).
+def mla_decode(query, paged_cache, block_table, lengths, scale, splits=8, workspace=None, output=None, lse=None, checked_pages=False):
+    """Paged decode (`dscuda_mla_decode`; `dscuda_mla_decode_checked` with `checked_pages`, which also
+    passes the number of cache pages so that a page number outside the cache is replaced and reported).
     query [B,1,H,576], paged_cache [blocks,page,1,576], block_table [B,pages] int32,
     lengths [B] int32 -> (output [B,1,H,512] bf16, lse [B,H,1] fp32)."""
     _require(query, paged_cache, block_table, lengths, workspace)
@@ -86,9 +87,14 @@ def mla_decode(query, paged_cache, block_table, lengths, scale, splits=8, worksp
     if lse is None:
         lse = torch.empty(b, h, 1, device=query.device, dtype=torch.float32)
     lib = library("mla")
-    checked(lib, "mla", lib.dscuda_mla_decode(
-        _ptr(output), _ptr(lse), _ptr(query), _ptr(paged_cache), _ptr(block_table), _ptr(lengths), _ptr(workspace),
-        b, h, rank, rope, page_size, block_table.shape[1], splits, scale, _stream()))
+    if checked_pages:
+        checked(lib, "mla", lib.dscuda_mla_decode_checked(
+            _ptr(output), _ptr(lse), _ptr(query), _ptr(paged_cache), _ptr(block_table), _ptr(lengths), _ptr(workspace),
+            b, h, rank, rope, page_size, block_table.shape[1], paged_cache.shape[0], splits, scale, _stream()))
+    else:
+        checked(lib, "mla", lib.dscuda_mla_decode(
+            _ptr(output), _ptr(lse), _ptr(query), _ptr(paged_cache), _ptr(block_table), _ptr(lengths), _ptr(workspace),
+            b, h, rank, rope, page_size, block_table.shape[1], splits, scale, _stream()))
     return output, lse
 
 

@@ -51,6 +51,16 @@ int dscuda_mla_decode(
     int batch, int heads, int rank, int rope, int page_size, int pages, int splits,
     float scale, void* stream);
 
+/* No counterpart in the reference (include/mla.h, mla_decode_forward_checked_cuda):
+ * dscuda_mla_decode plus the number of physical cache pages; a block-table entry
+ * outside [0, cache_blocks) is read as page 0 and sets the device status to 3. */
+int dscuda_mla_decode_checked(
+    void* output, float* lse,
+    const void* query, const void* paged_cache,
+    const int* block_table, const int* lengths, float* workspace,
+    int batch, int heads, int rank, int rope, int page_size, int pages, int cache_blocks, int splits,
+    float scale, void* stream);
+
 /* No counterpart in the reference: paged decode that takes no workspace and
  * allocates nothing.  For hosts that cannot allocate device memory where they
  * call from (fixed up-front memory pools, plugins inside a foreign allocator,
@@ -108,7 +118,7 @@ int dscuda_mla_prefill_backward(
 
 /* No counterpart in the reference: sticky device status of the MLA kernels
  * (0 fine, 1 a bounded in-kernel wait ran out, 2 misaligned shared memory, 3 a
- * cache append skipped an index outside the cache).  Synchronises the device. */
+ * cache append skipped, or a checked decode replaced, an index outside the cache).  Synchronises the device. */
 int dscuda_mla_device_status(int reset);
 
 /* reference: benchmarks/bindings/flash_attention_bridge.cu:13 */

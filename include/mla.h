@@ -75,9 +75,13 @@ std::size_t mla_decode_workspace_elements(
 
 // One packed BF16 query token [B,1,H,C+R] per sequence against a paged cache
 // [blocks,page,1,C+R]; block_table [B,pages_per_sequence] holds physical page
-// ids, cache_lengths [B] the number of valid tokens (>= 1).  output [B,1,H,C],
+// ids, cache_lengths [B] the number of valid tokens.  output [B,1,H,C],
 // logsumexp [B*H].  page_size must be a multiple of 64.  `splits` bounds how
 // many partial results per (sequence, head) the workspace can hold.
+// A length of 0 gives NaN output and -inf logsumexp for that sequence (the
+// softmax of an empty row); a length above pages_per_sequence * page_size is
+// read as that capacity.  Page numbers are trusted: this signature (the
+// reference's) does not carry the size of the cache.
 void mla_decode_forward_cuda(
     __nv_bfloat16* output,
     float* logsumexp,
@@ -92,6 +96,29 @@ void mla_decode_forward_cuda(
     int rope_size,
     int page_size,
     int pages_per_sequence,
+    int splits,
+    float scale,
+    cudaStream_t stream = nullptr);
+
+// No counterpart in the reference.  mla_decode_forward_cuda for callers that know
+// how many physical pages the cache has (`cache_blocks`): a block-table entry
+// outside [0, cache_blocks) is read as page 0 and sets the device status to 3
+// instead of reaching memory outside the cache.
+void mla_decode_forward_checked_cuda(
+    __nv_bfloat16* output,
+    float* logsumexp,
+    const __nv_bfloat16* query,
+    const __nv_bfloat16* paged_kv_cache,
+    const int* block_table,
+    const int* cache_lengths,
+    float* workspace,
+    int batch_size,
+    int heads,
+    int kv_rank,
+    int rope_size,
+    int page_size,
+    int pages_per_sequence,
+    int cache_blocks,
     int splits,
     float scale,
     cudaStream_t stream = nullptr);
@@ -254,8 +281,8 @@ void mla_rope_apply_cuda(
 
 // Sticky device status shared by the kernels above: 0 = fine, 1 = a bounded
 // pipeline wait inside a kernel ran out (results of that launch are invalid),
-// 2 = a kernel found its shared memory misaligned, 3 = a cache append skipped a
-// page number or position outside the cache.
+// 2 = a kernel found its shared memory misaligned, 3 = a cache append skipped (or
+// a checked decode replaced) a page number or position outside the cache.
 // Reading it synchronises the device; it is for tests and diagnosis, not for
 // the hot path.  `reset` clears it after reading.
 int mla_device_status(bool reset);

@@ -212,6 +212,58 @@ def prefill_backward(dout, output, lse, q_nope, q_pe, k_nope, k_pe, v, scale,
     return tuple(torch.cat([p[i][0] for p in parts], 0).contiguous() for i in range(4))
 
 
+def prefill_row_block(q_nope, q_pe, k_nope, k_pe, v, scale, rows, dout=None):
+    """The query rows `rows = (r0, r1)` of a dense causal problem without the full
+    S x S matrices: only the (r1-r0) x r1 score block is formed.  Same steps as
+    `_prefill_forward_dense` / `_prefill_backward_dense` (reference/python/mla.py:26-51)
+    restricted to those rows, so sequences of tens of thousands of tokens can be
+    checked on the CPU.
+
+    Tensors are dense [B,S,H,*].  Returns (O [B,r1-r0,H,128], LSE [B,H,r1-r0]) and,
+    when `dout` [B,S,H,128] is given, also dQ [B,r1-r0,H,192].
+    """
+    q_nope, q_pe, k_nope, k_pe, v = map(_compute, (q_nope, q_pe, k_nope, k_pe, v))
+    r0, r1 = rows
+    queries = torch.arange(r0, r1)[:, None]
+    mask = torch.arange(r1)[None, :] <= queries                                  # key k visible to query q iff k <= q
+    score = _prefill_scores(q_nope[:, r0:r1], q_pe[:, r0:r1], k_nope[:, :r1], k_pe[:, :r1], scale, mask)
+    lse = score.logsumexp(dim=-1)
+    probability = (score - lse.unsqueeze(-1)).exp()
+    output = torch.einsum("bhqk,bkhd->bqhd", probability, v[:, :r1])
+    if dout is None:
+        return output.contiguous(), lse.contiguous()
+    dout = _compute(dout)[:, r0:r1]
+    dprobability = torch.einsum("bqhd,bkhd->bhqk", dout, v[:, :r1])
+    delta = (dout * output).sum(dim=-1).transpose(1, 2).unsqueeze(-1)
+    dscore = probability * (dprobability - delta) * scale
+    dq = torch.cat((torch.einsum("bhqk,bkhc->bqhc", dscore, k_nope[:, :r1]),
+                    torch.einsum("bhqk,bkr->bqhr", dscore, k_pe[:, :r1, 0])), -1)
+    return output.contiguous(), lse.contiguous(), dq.contiguous()
+
+
+def prefill_key_block(dout, output, lse, q_nope, q_pe, k_nope, k_pe, v, scale, keys):
+    """The key rows `keys = (k0, k1)` of the closed-form backward without the full
+    S x S matrices: only the (S-k0) x (k1-k0) block (queries k0..S-1) is formed.
+    Same steps as `_prefill_backward_dense` (reference/python/mla.py:46-55).
+
+    Dense [B,S,H,*] tensors, `output` / `lse` [B,H,S] from the forward.  Returns
+    (dK_nope [B,k1-k0,H,128], dK_pe [B,k1-k0,1,64] summed over heads, dV [B,k1-k0,H,128]).
+    """
+    dout, output, q_nope, q_pe, k_nope, k_pe, v = map(_compute, (dout, output, q_nope, q_pe, k_nope, k_pe, v))
+    k0, k1 = keys
+    total = q_nope.shape[1]
+    mask = torch.arange(k0, k1)[None, :] <= torch.arange(k0, total)[:, None]
+    score = _prefill_scores(q_nope[:, k0:], q_pe[:, k0:], k_nope[:, k0:k1], k_pe[:, k0:k1], scale, mask)
+    probability = (score - lse[:, :, k0:].unsqueeze(-1)).exp()
+    dprobability = torch.einsum("bqhd,bkhd->bhqk", dout[:, k0:], v[:, k0:k1])
+    delta = (dout[:, k0:] * output[:, k0:]).sum(dim=-1).transpose(1, 2).unsqueeze(-1)
+    dscore = probability * (dprobability - delta) * scale
+    dk_nope = torch.einsum("bhqk,bqhc->bkhc", dscore, q_nope[:, k0:])
+    dv = torch.einsum("bhqk,bqhd->bkhd", probability, dout[:, k0:])
+    dk_pe = torch.einsum("bhqk,bqhr->bkr", dscore, q_pe[:, k0:])[:, :, None]
+    return dk_nope.contiguous(), dk_pe.contiguous(), dv.contiguous()
+
+
 # --------------------------------------------------------------------------
 # FlashAttention D=128 GQA forward (benchmarks/flash_attention.py:68-75)
 # --------------------------------------------------------------------------

@@ -116,3 +116,47 @@ def test_backward_matches_oracle(gpu, b, t, h):
     for name, got, ref in zip(("dquery", "dquery_rope", "dlatent", "dkey_rope"), grads, reference):
         assert rel_l2(got.cpu().float(), ref) <= 1e-2, name
         torch.testing.assert_close(got.cpu().float(), ref.bfloat16().float(), atol=1e-2, rtol=1e-2)
+
+
+def test_decode_empty_and_overlong_lengths(gpu):
+    """Length 0: NaN output and -inf LSE, as the softmax of an empty row gives in the reference
+    (reference/python/mla.py:36-38), whatever an earlier call left in the workspace.  A length above
+    the capacity of the block-table row is read as that capacity."""
+    from dscuda_b200 import mla
+    query, cache, table, lengths = oracle.decode_inputs(seed=77, batch=4, heads=16, low=100, high=100)     # 2 pages each
+    scale = 192 ** -.5
+    workspace = mla.decode_workspace(4, 16, 4, 512, gpu)
+    ref_out, ref_lse = oracle.paged_decode(query, cache, table, torch.tensor([100, 128, 100, 128], dtype=torch.int32), scale)
+    mla.mla_decode(query.to(gpu), cache.to(gpu), table.to(gpu), lengths.to(gpu), scale, splits=4, workspace=workspace)   # fills the workspace
+    odd = torch.tensor([100, 0, 100, 5000], dtype=torch.int32)
+    out, lse = mla.mla_decode(query.to(gpu), cache.to(gpu), table.to(gpu), odd.to(gpu), scale, splits=4, workspace=workspace)
+    torch.cuda.synchronize()
+    assert mla.device_status() == 0
+    out, lse = out.cpu().float(), lse.cpu()
+    assert bool(torch.isnan(out[1]).all()) and bool((lse[1] == float("-inf")).all())
+    for b in (0, 2, 3):
+        assert max_err_ratio(out[b], ref_out[b]) <= 1e-2
+        assert float((lse[b] - ref_lse[b]).abs().max()) <= 1e-3
+
+
+def test_checked_decode_reports_page_numbers_outside_the_cache(gpu):
+    from dscuda_b200 import mla
+    query, cache, table, lengths = oracle.decode_inputs(seed=78, batch=3, heads=128, low=200, high=600)
+    scale = 192 ** -.5
+    args = (query.to(gpu), cache.to(gpu))
+    out, lse = mla.mla_decode(*args, table.to(gpu), lengths.to(gpu), scale, splits=4, checked_pages=True)
+    torch.cuda.synchronize()
+    assert mla.device_status() == 0
+    ref_out, ref_lse = oracle.paged_decode(query, cache, table, lengths, scale)
+    assert max_err_ratio(out.cpu().float(), ref_out) <= 1e-2
+    assert float((lse.cpu() - ref_lse).abs().max()) <= 1e-3
+    bad = table.clone()
+    bad[1, 0] = cache.shape[0] + 1000
+    bad[2, 1] = -7
+    out, lse = mla.mla_decode(*args, bad.to(gpu), lengths.to(gpu), scale, splits=4, checked_pages=True)
+    torch.cuda.synchronize()
+    assert mla.device_status(reset=True) == 3
+    assert mla.device_status() == 0
+    # the sequence with a clean table row is unaffected; the others are finite (page 0 was read instead)
+    assert max_err_ratio(out.cpu().float()[0], ref_out[0]) <= 1e-2
+    assert bool(torch.isfinite(out.float()).all())

@@ -121,3 +121,24 @@ def test_seeded_config_generators_are_stable():
     assert q.shape == (4, 1, 8, 576) and cache.shape[1:] == (64, 1, 576)
     used = torch.cat([table[i, : (int(lens[i]) + 63) // 64] for i in range(4)])
     assert used.unique().numel() == used.numel() == cache.shape[0]
+
+
+@pytest.mark.parametrize("rows,keys", [((0, 50), (0, 50)), ((37, 90), (0, 31)), ((60, 90), (41, 77))])
+def test_block_helpers_equal_the_dense_restatement(rows, keys):
+    """`prefill_row_block` / `prefill_key_block` (used to check sequences of tens of thousands of tokens)
+    are slices of the dense restatement."""
+    q_nope, q_pe, k_nope, k_pe, v, dout = oracle.prefill_inputs(11, 2, 90, 3, dtype=torch.float32, dout_std=0.1)
+    inputs = (q_nope, q_pe, k_nope, k_pe, v)
+    scale = 192 ** -0.5
+    out, lse = oracle.prefill_forward(*inputs, scale)
+    dq, dk_nope, dk_pe, dv = oracle.prefill_backward(dout, out, lse, *inputs, scale)
+    r0, r1 = rows
+    b_out, b_lse, b_dq = oracle.prefill_row_block(*inputs, scale, rows, dout)
+    torch.testing.assert_close(b_out, out[:, r0:r1], atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(b_lse, lse[:, :, r0:r1], atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(b_dq, dq[:, r0:r1], atol=1e-5, rtol=1e-5)
+    k0, k1 = keys
+    b_dk, b_dkpe, b_dv = oracle.prefill_key_block(dout, out, lse, *inputs, scale, keys)
+    torch.testing.assert_close(b_dk, dk_nope[:, k0:k1], atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(b_dkpe, dk_pe[:, k0:k1], atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(b_dv, dv[:, k0:k1], atol=1e-5, rtol=1e-5)
