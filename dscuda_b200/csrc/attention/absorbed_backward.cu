@@ -1,260 +1,821 @@
 // Backward of the absorbed-latent causal MLA forward
-// (mla_compressed_attention_backward_cuda).  The interface gives no scratch
-// memory and the gradients of the shared latent / rotary key sum over every
-// head and every later query, so the work is split the way the reference splits
-// it (kernels/attention/mla/sm89.cu:295,356): one pass owns the query-side
-// rows, one pass owns the key-side rows, and each recomputes P from the saved
-// LSE.  Unlike the reference, a warp (not a CTA) owns a row, the opposite side
-// streams through shared memory in tiles shared by the 8 warps of a CTA, and the
-// row-sum delta = dO.O is computed once per row instead of once per pair.
+// (mla_compressed_attention_backward_cuda) on the sm_100a tensor cores.
 //
-// These are CUDA-core kernels (fp32 FMA, warp-shuffle reductions): the 576-wide
-// output rows leave no room in tensor memory for a tcgen05 formulation without
-// scratch, and the sizes this entry point sees in the reference's harness
-// (T <= 512, H <= 8) are far from tensor-bound.
+// The interface gives no scratch memory, the gradients of the shared latent /
+// rotary key sum over every head and every later query, and the operands are wide
+// (576 score columns, 512 value columns), so the work is split the way the
+// reference splits it (kernels/attention/mla/sm89.cu:295 query side, :356 key
+// side): one kernel owns the key-side gradients, one owns the query-side
+// gradients, and each recomputes P from the saved LSE.  Both are tcgen05 kernels
+// and share one tile shape: a score tile is S^T = K Q^T with 128 keys on the
+// tensor-memory lanes and 64 (token, head) rows on the columns, so that one
+// thread owns one key, the per-row constants (LSE, delta, token index) are read
+// from shared memory, and P^T / dS^T come out in the form the gradient products
+// want.  Wide operands stream through shared memory in 64-column chunks.
+//
+// One call launches, on the caller's stream:
+//   1. absorbed_delta_kernel: delta[row] = sum_c dO[row,c] O[row,c], kept in the
+//      first four bytes of each dquery_rope row (an output the last kernel
+//      overwrites, so no scratch is needed);
+//   2. absorbed_backward_key_kernel: CTA = (128-key tile, one 256-column half of
+//      dlatent).  The key tile (9 chunks, 144 KB) stays in shared memory; every
+//      64-row tile at or after the diagonal streams by twice: its 17 chunks of
+//      query_latent | query_rope | dO for S^T and dP^T = latent dO^T, and after the
+//      softmax the 9 chunks this half needs again, as the B operand of
+//      dlatent += P^T dO + dS^T query_latent and dkey_rope += dS^T query_rope
+//      (P^T and dS^T are bf16 A operands in tensor memory).  Single writer per
+//      output element, no atomics;
+//   3. absorbed_backward_query_kernel: CTA = 64 (token, head) rows, resident as the
+//      B operands query_latent | query_rope | dO (136 KB); every 128-key tile up
+//      to the diagonal streams by twice: for S^T / dP^T, and again as the
+//      MN-major A operand of dQ^T += K^T dS^T (output columns on the lanes, rows on
+//      the columns; dS^T goes through shared memory as the B operand).
+//
+// Warps 0-7: softmax (thread = key x 32 of the 64 rows); warp 8: MMA issue (whole
+// warp, one elected lane executes); warp 9: TMA loads.  Every wait is bounded.
 #include "mla.h"
 #include "cuda_common.h"
 #include "attention_internal.h"
+#include "sm100_primitives.cuh"
+#include "../common/tensor_map.h"
 
+#include <cstddef>
 #include <cstdint>
 #include <stdexcept>
 
 namespace dscuda {
 namespace {
 
-constexpr int RANK = MLA_KV_RANK;       // 512
-constexpr int ROPE = MLA_ROPE_SIZE;     // 64
-constexpr int WIDTH = RANK + ROPE;      // 576
-constexpr int PAIRS = WIDTH / 64;       // 9 bf16 pairs per lane: pair i covers columns 64*i + 2*lane, +1
-constexpr int LATENT_PAIRS = RANK / 64; // the first 8 pairs are latent (they double as V), the last is rotary
-constexpr int WARPS = 8;
-constexpr int THREADS = WARPS * 32;
-constexpr int KEY_TILE = 32;            // keys staged per step in the query-side kernel
-constexpr int ROW_TILE = 16;            // (token, head) rows staged per step in the key-side kernel
+using namespace sm100;
 
-__device__ __forceinline__ float warp_sum(float value) {
-#pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) {
-        value += __shfl_xor_sync(0xffffffffU, value, offset);
-    }
-    return value;
+constexpr int RANK = MLA_KV_RANK;             // 512
+constexpr int ROPE = MLA_ROPE_SIZE;           // 64
+constexpr int CHUNKS = (RANK + ROPE) / 64;    // 9 column chunks of 64; chunk 8 is the rotary part
+constexpr int LATENT_CHUNKS = RANK / 64;      // 8
+constexpr int KEYS = 128;                     // keys per tile = MMA M = tensor-memory lanes
+constexpr int ROWS = 64;                      // (token, head) rows per tile = MMA N
+constexpr int KEY_CHUNK = KEYS * 128;         // 16 KB: [128 keys x 64 bf16]
+constexpr int ROW_CHUNK = ROWS * 128;         //  8 KB: [64 rows x 64 bf16]
+constexpr int THREADS = 320;
+constexpr int MMA_WARP = 8;
+constexpr int LOAD_WARP = 9;
+constexpr int TMEM_COLUMNS = 512;
+constexpr int MISC_BYTES = 2048;
+constexpr float LOG2E = 1.4426950408889634F;
+
+__device__ int absorbed_backward_status = 0;
+
+struct AbsorbedBackwardParams {
+    CUtensorMap q_lat;      // [B*T*H, 512] box 64 x 64
+    CUtensorMap q_rope;     // [B*T*H, 64]  box 64 x 64
+    CUtensorMap d_out;      // [B*T*H, 512] box 64 x 64
+    CUtensorMap k_lat;      // [B*T, 512]   box 128 x 64
+    CUtensorMap k_rope;     // [B*T, 64]    box 128 x 64
+    __nv_bfloat16* dq_lat;  // [B,T,H,512]
+    __nv_bfloat16* dq_rope; // [B,T,H,64]; the first float of each row holds delta until the query kernel overwrites it
+    __nv_bfloat16* dlatent; // [B,T,512]
+    __nv_bfloat16* dk_rope; // [B,T,64]
+    const float* lse;       // [B,H,T]
+    int batch;
+    int sequence;
+    int heads;
+    float scale;
+    float scale_log2;
+};
+
+// Per-row constants of a 64-row tile, written by the load warp, read by every softmax thread.
+struct RowConstants {
+    alignas(16) float lse2[ROWS];     // LSE * log2 e
+    alignas(16) float delta[ROWS];
+    alignas(16) int token[ROWS];      // token index of the row, -1 for rows past the end of the sequence
+};
+
+__device__ __forceinline__ float stored_delta(const AbsorbedBackwardParams& p, size_t global_row) {
+    return *reinterpret_cast<const float*>(p.dq_rope + global_row * ROPE);
 }
 
-__device__ __forceinline__ float2 load_pair(const __nv_bfloat16* base) {
-    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(base));
+// Lanes of one warp fill the constants of rows [row0, row0 + 64) of sequence `b`.
+__device__ __forceinline__ void fill_row_constants(const AbsorbedBackwardParams& p, RowConstants& rc, int b, int row0, int lane) {
+    const int rows_per_sequence = p.sequence * p.heads;
+#pragma unroll
+    for (int e = 0; e < ROWS / 32; ++e) {
+        const int n = e * 32 + lane;
+        const int row = row0 + n;
+        float lse_value = 0.0F, delta_value = 0.0F;
+        int token = -1;
+        if (row < rows_per_sequence) {
+            token = row / p.heads;
+            const int head = row - token * p.heads;
+            lse_value = p.lse[(static_cast<size_t>(b) * p.heads + head) * p.sequence + token] * LOG2E;
+            delta_value = stored_delta(p, static_cast<size_t>(b) * rows_per_sequence + row);
+        }
+        rc.lse2[n] = lse_value;
+        rc.delta[n] = delta_value;
+        rc.token[n] = token;
+    }
 }
 
-// Loads the 9 column pairs of one 576-wide row whose latent and rotary parts
-// live in two tensors.
-__device__ __forceinline__ void load_row(float2 (&dst)[PAIRS], const __nv_bfloat16* latent_row, const __nv_bfloat16* rope_row, int lane) {
+// One thread's share of a score tile: key `key_pos` (its tensor-memory lane) against 32 of the
+// tile's 64 rows.  Reads S^T and dP^T (fp32) from tensor memory and returns P^T and
+// dS^T = P^T (dP^T - delta) scale as packed bf16 pairs.  A key is visible to a row when
+// key_pos <= token(row); rows past the end have token -1.
+__device__ __forceinline__ void score_tile_share(const AbsorbedBackwardParams& p, uint32_t st_tmem, uint32_t dpt_tmem, const RowConstants& rc,
+                                                 int group, int key_pos, bool masked, uint32_t (&p_packed)[16], uint32_t (&ds_packed)[16]) {
+    uint32_t sb[32];
+    float prob[32];
+    tmem_ld_x32(st_tmem, sb);
+    tmem_wait_ld();
+    const float4* lse4 = reinterpret_cast<const float4*>(rc.lse2 + group * 32);
+    const float4* delta4 = reinterpret_cast<const float4*>(rc.delta + group * 32);
+    const int4* token4 = reinterpret_cast<const int4*>(rc.token + group * 32);
 #pragma unroll
-    for (int i = 0; i < LATENT_PAIRS; ++i) {
-        dst[i] = load_pair(latent_row + 64 * i + 2 * lane);
+    for (int n = 0; n < 32; n += 4) {
+        const float4 l = lse4[n / 4];
+        prob[n] = exp2_approx(fmaf(__uint_as_float(sb[n]), p.scale_log2, -l.x));
+        prob[n + 1] = exp2_approx(fmaf(__uint_as_float(sb[n + 1]), p.scale_log2, -l.y));
+        prob[n + 2] = exp2_approx(fmaf(__uint_as_float(sb[n + 2]), p.scale_log2, -l.z));
+        prob[n + 3] = exp2_approx(fmaf(__uint_as_float(sb[n + 3]), p.scale_log2, -l.w));
     }
-    dst[LATENT_PAIRS] = load_pair(rope_row + 2 * lane);
+    if (masked) {
+#pragma unroll
+        for (int n = 0; n < 32; n += 4) {
+            const int4 t = token4[n / 4];
+            prob[n] = key_pos <= t.x ? prob[n] : 0.0F;
+            prob[n + 1] = key_pos <= t.y ? prob[n + 1] : 0.0F;
+            prob[n + 2] = key_pos <= t.z ? prob[n + 2] : 0.0F;
+            prob[n + 3] = key_pos <= t.w ? prob[n + 3] : 0.0F;
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < 32; n += 2) {
+        p_packed[n / 2] = pack_bf16x2(prob[n], prob[n + 1]);
+    }
+    tmem_ld_x32(dpt_tmem, sb);
+    tmem_wait_ld();
+#pragma unroll
+    for (int n = 0; n < 32; n += 4) {
+        const float4 d = delta4[n / 4];
+        ds_packed[n / 2] = pack_bf16x2(prob[n] * (__uint_as_float(sb[n]) - d.x) * p.scale, prob[n + 1] * (__uint_as_float(sb[n + 1]) - d.y) * p.scale);
+        ds_packed[n / 2 + 1] =
+            pack_bf16x2(prob[n + 2] * (__uint_as_float(sb[n + 2]) - d.z) * p.scale, prob[n + 3] * (__uint_as_float(sb[n + 3]) - d.w) * p.scale);
+    }
+}
+
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const uint32_t* values) {
+#pragma unroll
+    for (int e = 0; e < 32; e += 8) {
+        uint4 vec;
+        vec.x = pack_bf16x2(__uint_as_float(values[e]), __uint_as_float(values[e + 1]));
+        vec.y = pack_bf16x2(__uint_as_float(values[e + 2]), __uint_as_float(values[e + 3]));
+        vec.z = pack_bf16x2(__uint_as_float(values[e + 4]), __uint_as_float(values[e + 5]));
+        vec.w = pack_bf16x2(__uint_as_float(values[e + 6]), __uint_as_float(values[e + 7]));
+        *reinterpret_cast<uint4*>(dst + e) = vec;
+    }
 }
 
 // ---------------------------------------------------------------------------
-// Query side: one warp per (token, head) row.
+// delta[row] = sum_c dO[row,c] * O[row,c]; one warp per (token, head) row.  The result is parked
+// in the first four bytes of the row's dquery_rope output.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(THREADS) absorbed_backward_query_kernel(
-    __nv_bfloat16* dq_latent, __nv_bfloat16* dq_rope, const __nv_bfloat16* dout, const __nv_bfloat16* out, const float* lse,
-    const __nv_bfloat16* q_latent, const __nv_bfloat16* q_rope, const __nv_bfloat16* kv_latent, const __nv_bfloat16* k_rope,
-    int sequence, int heads, float scale) {
-    __shared__ __align__(16) __nv_bfloat16 keys[KEY_TILE][WIDTH];
+__global__ void __launch_bounds__(256) absorbed_delta_kernel(__nv_bfloat16* dq_rope, const __nv_bfloat16* dout, const __nv_bfloat16* out,
+                                                             size_t rows) {
+    const int lane = threadIdx.x % 32;
+    const size_t warp_stride = static_cast<size_t>(gridDim.x) * (blockDim.x / 32);
+    for (size_t row = static_cast<size_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32; row < rows; row += warp_stride) {
+        float sum = 0.0F;
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+            const uint4 a = __ldg(reinterpret_cast<const uint4*>(dout + row * RANK) + part * 32 + lane);
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(out + row * RANK) + part * 32 + lane);
+            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 x = __bfloat1622float2(a2[e]), y = __bfloat1622float2(b2[e]);
+                sum += x.x * y.x + x.y * y.y;
+            }
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            sum += __shfl_xor_sync(0xffffffffU, sum, offset);
+        }
+        if (lane == 0) {
+            *reinterpret_cast<float*>(dq_rope + row * ROPE) = sum;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Key side.  Tensor memory: dlatent half 0..255, dkey_rope 256..319, S^T 320..383 (P^T overwrites
+// it as bf16), dP^T 384..447 (dS^T likewise).  Shared memory: the key tile (9 x 16 KB), a ring of
+// five 16 KB units, constants.  A unit is one TMA transaction of one or two 8 KB row chunks.
+// Per row tile, in this order: 4 units of query_latent chunk pairs, 1 of query_rope, 4 of dO
+// pairs (S^T and dP^T); then, after the softmax, 2 units of this half's dO pairs, 2 of its
+// query_latent pairs and 1 of query_rope (the gradient products).
+// ---------------------------------------------------------------------------
+namespace ks {
+constexpr int RING_SLOTS = 5;
+constexpr int SLOT_BYTES = 2 * ROW_CHUNK;
+constexpr int RESIDENT_BYTES = CHUNKS * KEY_CHUNK;
+constexpr int SMEM_BYTES = RESIDENT_BYTES + RING_SLOTS * SLOT_BYTES + MISC_BYTES + 1024;
+constexpr int UNITS_PER_TILE = 14;
+constexpr uint32_t TMEM_DLAT = 0;
+constexpr uint32_t TMEM_DROPE = 256;
+constexpr uint32_t TMEM_X0 = 320;
+constexpr uint32_t TMEM_X1 = 384;
+static_assert(SMEM_BYTES <= 232448, "key-side shared memory");
+
+struct Shared {
+    uint64_t resident_full;
+    uint64_t unit_full[RING_SLOTS];
+    uint64_t unit_empty[RING_SLOTS];
+    uint64_t rows_ready[2];
+    uint64_t s_ready;           // tensor core -> softmax: S^T and dP^T of the tile are complete
+    uint64_t p_ready;           // 256 softmax threads: P^T and dS^T are stored
+    uint64_t final_full;
+    uint32_t tmem_base;
+    int abort_flag;
+    int masked[2];
+    RowConstants rows[2];
+};
+static_assert(sizeof(Shared) <= MISC_BYTES, "key-side barrier block too large");
+}  // namespace ks
+
+__global__ void __launch_bounds__(THREADS, 1) absorbed_backward_key_kernel(const __grid_constant__ AbsorbedBackwardParams p) {
+    using namespace ks;
+    extern __shared__ uint8_t smem_raw[];
+    if (*reinterpret_cast<volatile int*>(&absorbed_backward_status) == STATUS_WAIT_TIMEOUT) {
+        return;
+    }
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
-    const int b = blockIdx.y;
-    const int rows = sequence * heads;
-    const int first_row = blockIdx.x * WARPS;
-    const int row = first_row + warp;
-    const bool active = row < rows;
-    const int token = active ? row / heads : 0;
-    const int head = active ? row % heads : 0;
-    const int last_token = min(rows - 1, first_row + WARPS - 1) / heads;   // furthest key any warp of the CTA needs
+    const int b = blockIdx.z;
+    const int half = blockIdx.y;                         // which 256 columns of dlatent
+    const int key_start = blockIdx.x * KEYS;             // tile 0 meets the most rows: longest first
+    const int rows_per_sequence = p.sequence * p.heads;
+    const int first_tile = static_cast<int>((static_cast<long long>(key_start) * p.heads) / ROWS);
+    const int tile_count = (rows_per_sequence + ROWS - 1) / ROWS - first_tile;
 
-    float2 q[PAIRS], grad[PAIRS], d_out[LATENT_PAIRS];
-    float delta = 0.0F, row_lse = 0.0F;
-#pragma unroll
-    for (int i = 0; i < PAIRS; ++i) {
-        q[i] = make_float2(0.0F, 0.0F);
-        grad[i] = make_float2(0.0F, 0.0F);
-    }
-    if (active) {
-        const size_t global_row = static_cast<size_t>(b) * rows + row;
-        load_row(q, q_latent + global_row * RANK, q_rope + global_row * ROPE, lane);
-        float partial = 0.0F;
-#pragma unroll
-        for (int i = 0; i < LATENT_PAIRS; ++i) {
-            d_out[i] = load_pair(dout + global_row * RANK + 64 * i + 2 * lane);
-            const float2 o = load_pair(out + global_row * RANK + 64 * i + 2 * lane);
-            partial += d_out[i].x * o.x + d_out[i].y * o.y;
-        }
-        delta = warp_sum(partial);
-        row_lse = lse[(static_cast<size_t>(b) * heads + head) * sequence + token];
-    } else {
-#pragma unroll
-        for (int i = 0; i < LATENT_PAIRS; ++i) {
-            d_out[i] = make_float2(0.0F, 0.0F);
-        }
-    }
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023U) & ~1023U;
+    uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t k_smem = smem_base;
+    const uint32_t ring = smem_base + RESIDENT_BYTES;
+    Shared* sh = reinterpret_cast<Shared*>(smem_aligned + RESIDENT_BYTES + RING_SLOTS * SLOT_BYTES);
+    volatile int* abort_flag = &sh->abort_flag;
 
-    for (int key0 = 0; key0 <= last_token; key0 += KEY_TILE) {
-        const int tile_keys = min(KEY_TILE, last_token + 1 - key0);
-        __syncthreads();
-        // stage [tile_keys x 576] as 16-byte vectors: 64 per latent row, 8 per rotary row
-        for (int index = threadIdx.x; index < tile_keys * 72; index += THREADS) {
-            const int k = index / 72;
-            const int v = index % 72;
-            const size_t key_row = static_cast<size_t>(b) * sequence + key0 + k;
-            const uint4 value = v < 64 ? reinterpret_cast<const uint4*>(kv_latent + key_row * RANK)[v]
-                                       : reinterpret_cast<const uint4*>(k_rope + key_row * ROPE)[v - 64];
-            reinterpret_cast<uint4*>(&keys[k][0])[v] = value;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&sh->resident_full), 1);
+        for (int i = 0; i < RING_SLOTS; ++i) {
+            mbar_init(smem_u32(&sh->unit_full[i]), 1);
+            mbar_init(smem_u32(&sh->unit_empty[i]), 1);
         }
-        __syncthreads();
-        const int visible = active ? min(tile_keys, token + 1 - key0) : 0;     // causal: key <= token
-        for (int k = 0; k < visible; ++k) {
-            float2 kv[PAIRS];
-            float s = 0.0F, dp = 0.0F;
-#pragma unroll
-            for (int i = 0; i < PAIRS; ++i) {
-                kv[i] = load_pair(&keys[k][64 * i + 2 * lane]);
-                s += q[i].x * kv[i].x + q[i].y * kv[i].y;
+        mbar_init(smem_u32(&sh->rows_ready[0]), 1);
+        mbar_init(smem_u32(&sh->rows_ready[1]), 1);
+        mbar_init(smem_u32(&sh->s_ready), 1);
+        mbar_init(smem_u32(&sh->p_ready), 256);
+        mbar_init(smem_u32(&sh->final_full), 1);
+        sh->abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc(smem_u32(&sh->tmem_base), TMEM_COLUMNS);
+        tmem_relinquish();
+    }
+    if (warp == LOAD_WARP && lane == 0) {
+        tma_prefetch_descriptor(&p.q_lat);
+        tma_prefetch_descriptor(&p.q_rope);
+        tma_prefetch_descriptor(&p.d_out);
+        tma_prefetch_descriptor(&p.k_lat);
+        tma_prefetch_descriptor(&p.k_rope);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&sh->tmem_base);
+
+    if (warp == LOAD_WARP) {
+        // =================== TMA producer ===================================
+        if (lane == 0) {
+            const uint32_t bar = smem_u32(&sh->resident_full);
+            mbar_arrive_expect_tx(bar, RESIDENT_BYTES);
+            const int y = b * p.sequence + key_start;
+            for (int c = 0; c < LATENT_CHUNKS; ++c) {
+                tma_load_2d(k_smem + c * KEY_CHUNK, &p.k_lat, bar, c * 64, y);
             }
-#pragma unroll
-            for (int i = 0; i < LATENT_PAIRS; ++i) {
-                dp += d_out[i].x * kv[i].x + d_out[i].y * kv[i].y;
-            }
-            s = warp_sum(s);
-            dp = warp_sum(dp);
-            const float probability = __expf(s * scale - row_lse);
-            const float ds = probability * (dp - delta) * scale;
-#pragma unroll
-            for (int i = 0; i < PAIRS; ++i) {
-                grad[i].x += ds * kv[i].x;
-                grad[i].y += ds * kv[i].y;
-            }
+            tma_load_2d(k_smem + LATENT_CHUNKS * KEY_CHUNK, &p.k_rope, bar, 0, y);
         }
-    }
-    if (active) {
-        const size_t global_row = static_cast<size_t>(b) * rows + row;
-#pragma unroll
-        for (int i = 0; i < LATENT_PAIRS; ++i) {
-            *reinterpret_cast<__nv_bfloat162*>(dq_latent + global_row * RANK + 64 * i + 2 * lane) = __float22bfloat162_rn(grad[i]);
-        }
-        *reinterpret_cast<__nv_bfloat162*>(dq_rope + global_row * ROPE + 2 * lane) = __float22bfloat162_rn(grad[LATENT_PAIRS]);
-    }
-}
-
-// ---------------------------------------------------------------------------
-// Key side: one warp per key; every (token >= key, head) row contributes.
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(THREADS) absorbed_backward_key_kernel(
-    __nv_bfloat16* dkv_latent, __nv_bfloat16* dk_rope, const __nv_bfloat16* dout, const __nv_bfloat16* out, const float* lse,
-    const __nv_bfloat16* q_latent, const __nv_bfloat16* q_rope, const __nv_bfloat16* kv_latent, const __nv_bfloat16* k_rope,
-    int sequence, int heads, float scale) {
-    __shared__ __align__(16) __nv_bfloat16 queries[ROW_TILE][WIDTH];
-    __shared__ __align__(16) __nv_bfloat16 gradients[ROW_TILE][RANK];
-    __shared__ float row_lse[ROW_TILE];
-    __shared__ float row_delta[ROW_TILE];
-    const int warp = threadIdx.x / 32;
-    const int lane = threadIdx.x % 32;
-    const int b = blockIdx.y;
-    const int rows = sequence * heads;
-    const int first_key = blockIdx.x * WARPS;
-    const int key = first_key + warp;
-    const bool active = key < sequence;
-
-    float2 kv[PAIRS], grad[PAIRS];
-#pragma unroll
-    for (int i = 0; i < PAIRS; ++i) {
-        kv[i] = make_float2(0.0F, 0.0F);
-        grad[i] = make_float2(0.0F, 0.0F);
-    }
-    if (active) {
-        const size_t key_row = static_cast<size_t>(b) * sequence + key;
-        load_row(kv, kv_latent + key_row * RANK, k_rope + key_row * ROPE, lane);
-    }
-
-    for (int row0 = first_key * heads; row0 < rows; row0 += ROW_TILE) {
-        const int tile_rows = min(ROW_TILE, rows - row0);
-        __syncthreads();
-        // each warp stages two rows and computes their delta on the way
-        for (int r = warp; r < tile_rows; r += WARPS) {
-            const int row = row0 + r;
-            const size_t global_row = static_cast<size_t>(b) * rows + row;
-            float partial = 0.0F;
-#pragma unroll
-            for (int i = 0; i < LATENT_PAIRS; ++i) {
-                const __nv_bfloat162 qv = *reinterpret_cast<const __nv_bfloat162*>(q_latent + global_row * RANK + 64 * i + 2 * lane);
-                const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(dout + global_row * RANK + 64 * i + 2 * lane);
-                const float2 o = load_pair(out + global_row * RANK + 64 * i + 2 * lane);
-                const float2 g = __bfloat1622float2(gv);
-                partial += g.x * o.x + g.y * o.y;
-                *reinterpret_cast<__nv_bfloat162*>(&queries[r][64 * i + 2 * lane]) = qv;
-                *reinterpret_cast<__nv_bfloat162*>(&gradients[r][64 * i + 2 * lane]) = gv;
-            }
-            *reinterpret_cast<__nv_bfloat162*>(&queries[r][RANK + 2 * lane]) =
-                *reinterpret_cast<const __nv_bfloat162*>(q_rope + global_row * ROPE + 2 * lane);
-            partial = warp_sum(partial);
+        bool alive = true;
+        int unit = 0;                                    // units issued so far
+        for (int t = 0; t < tile_count && alive; ++t) {
+            const int row0 = (first_tile + t) * ROWS;
+            // The constants of tile t-2 (same buffer) were last read before P^T(t-2) was stored,
+            // and the ring (5 units) cannot run a whole tile (14 units) ahead of the tensor core.
+            fill_row_constants(p, sh->rows[t & 1], b, row0, lane);
             if (lane == 0) {
-                row_delta[r] = partial;
-                row_lse[r] = lse[(static_cast<size_t>(b) * heads + row % heads) * sequence + row / heads];
+                sh->masked[t & 1] = (row0 / p.heads < key_start + KEYS - 1 || row0 + ROWS > rows_per_sequence) ? 1 : 0;
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&sh->rows_ready[t & 1]));
+                const int y = b * rows_per_sequence + row0;
+                for (int u = 0; u < UNITS_PER_TILE && alive; ++u, ++unit) {
+                    const int slot = unit % RING_SLOTS;
+                    if (unit >= RING_SLOTS) {
+                        alive = mbar_wait(smem_u32(&sh->unit_empty[slot]), (unit / RING_SLOTS - 1) & 1, abort_flag, &absorbed_backward_status);
+                        if (!alive) {
+                            break;
+                        }
+                    }
+                    const uint32_t full = smem_u32(&sh->unit_full[slot]);
+                    const uint32_t dst = ring + slot * SLOT_BYTES;
+                    // which tensor and which chunk pair this unit carries
+                    const CUtensorMap* map;
+                    int chunk;                           // first chunk; -1: the single rotary chunk
+                    if (u < 4) {
+                        map = &p.q_lat, chunk = 2 * u;
+                    } else if (u == 4) {
+                        map = &p.q_rope, chunk = -1;
+                    } else if (u < 9) {
+                        map = &p.d_out, chunk = 2 * (u - 5);
+                    } else if (u < 11) {
+                        map = &p.d_out, chunk = 4 * half + 2 * (u - 9);
+                    } else if (u < 13) {
+                        map = &p.q_lat, chunk = 4 * half + 2 * (u - 11);
+                    } else {
+                        map = &p.q_rope, chunk = -1;
+                    }
+                    if (chunk < 0) {
+                        mbar_arrive_expect_tx(full, ROW_CHUNK);
+                        tma_load_2d(dst, map, full, 0, y);
+                    } else {
+                        mbar_arrive_expect_tx(full, 2 * ROW_CHUNK);
+                        tma_load_2d(dst, map, full, chunk * 64, y);
+                        tma_load_2d(dst + ROW_CHUNK, map, full, (chunk + 1) * 64, y);
+                    }
+                }
+            }
+            alive = __shfl_sync(0xffffffffU, alive ? 1 : 0, 0) != 0;
+            unit = __shfl_sync(0xffffffffU, unit, 0);
+        }
+    } else if (warp == MMA_WARP) {
+        // =================== MMA issuer (whole warp, elected lane executes) ==
+        const uint32_t leader = elect_one();
+        constexpr uint32_t IDESC_SCORE = make_idesc_bf16(KEYS, ROWS, false, false);
+        constexpr uint32_t IDESC_GRAD = make_idesc_bf16(KEYS, 128, false, true);      // B = two row chunks side by side, MN-major
+        constexpr uint32_t IDESC_ROPE = make_idesc_bf16(KEYS, 64, false, true);
+        bool alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->resident_full), 0, abort_flag, &absorbed_backward_status));
+        int unit = 0;
+        auto wait_unit = [&]() -> uint32_t {
+            const int slot = unit % RING_SLOTS;
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->unit_full[slot]), (unit / RING_SLOTS) & 1, abort_flag, &absorbed_backward_status));
+            tc_fence_after_sync();
+            return ring + slot * SLOT_BYTES;
+        };
+        auto release_unit = [&]() {
+            mma_commit_elect(smem_u32(&sh->unit_empty[unit % RING_SLOTS]), leader);
+            ++unit;
+        };
+        for (int t = 0; t < tile_count && alive; ++t) {
+            // ---- S^T = K Q^T (9 chunks), dP^T = latent dO^T (8 chunks) ----
+            for (int u = 0; u < 9 && alive; ++u) {
+                const uint32_t src = wait_unit();
+                if (!alive) {
+                    break;
+                }
+                const bool is_dout = u >= 5;
+                const int first_chunk = u < 4 ? 2 * u : (u == 4 ? LATENT_CHUNKS : 2 * (u - 5));
+                const int chunks_here = u == 4 ? 1 : 2;
+                const uint32_t acc = tmem_base + (is_dout ? TMEM_X1 : TMEM_X0);
+                for (int cc = 0; cc < chunks_here; ++cc) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const bool first = (u == 0 || u == 5) && cc == 0 && k == 0;
+                        mma_ss_elect(acc, make_kmajor_desc(k_smem + (first_chunk + cc) * KEY_CHUNK + k * 32),
+                                     make_kmajor_desc(src + cc * ROW_CHUNK + k * 32), IDESC_SCORE, first ? 0U : 1U, leader);
+                    }
+                }
+                release_unit();
+            }
+            if (!alive) {
+                break;
+            }
+            mma_commit_elect(smem_u32(&sh->s_ready), leader);
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->p_ready), t & 1, abort_flag, &absorbed_backward_status));
+            if (!alive) {
+                break;
+            }
+            tc_fence_after_sync();
+            // ---- dlatent half += P^T dO + dS^T query_latent; dkey_rope += dS^T query_rope ----
+            for (int u = 9; u < UNITS_PER_TILE && alive; ++u) {
+                const uint32_t src = wait_unit();
+                if (!alive) {
+                    break;
+                }
+                if (u < 13) {
+                    const uint32_t operand = tmem_base + (u < 11 ? TMEM_X0 : TMEM_X1);       // P^T for dO, dS^T for query_latent
+                    const uint32_t acc = tmem_base + TMEM_DLAT + ((u - 9) & 1) * 128;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        mma_ts_elect(acc, operand + (k / 2) * 32 + (k % 2) * 8, make_smem_desc(src + k * 2048, ROW_CHUNK, 1024), IDESC_GRAD,
+                                     (u >= 11 || t != 0 || k != 0) ? 1U : 0U, leader);
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        mma_ts_elect(tmem_base + TMEM_DROPE, tmem_base + TMEM_X1 + (k / 2) * 32 + (k % 2) * 8, make_smem_desc(src + k * 2048, ROW_CHUNK, 1024),
+                                     IDESC_ROPE, (t | k) != 0 ? 1U : 0U, leader);
+                    }
+                }
+                release_unit();
             }
         }
-        __syncthreads();
-        if (!active) {
-            continue;
+        if (alive) {
+            mma_commit_elect(smem_u32(&sh->final_full), leader);
         }
-        for (int r = 0; r < tile_rows; ++r) {
-            const int token = (row0 + r) / heads;
-            if (token < key) {          // causal: this query does not see the key
-                continue;
+    } else {
+        // =================== softmax: thread = (key, 32 of the 64 rows) ======
+        const int group = warp / 4;
+        const int r = threadIdx.x % KEYS;
+        const uint32_t lane_base = static_cast<uint32_t>((warp % 4) * 32) << 16;
+        const int key_pos = key_start + r;
+        const uint32_t st_tmem = tmem_base + lane_base + TMEM_X0 + group * 32;
+        const uint32_t dpt_tmem = tmem_base + lane_base + TMEM_X1 + group * 32;
+        bool alive = true;
+        for (int t = 0; t < tile_count; ++t) {
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->rows_ready[t & 1]), (t >> 1) & 1, abort_flag, &absorbed_backward_status) &&
+                                                mbar_wait(smem_u32(&sh->s_ready), t & 1, abort_flag, &absorbed_backward_status));
+            if (!alive) {
+                break;
             }
-            float2 qv[PAIRS], gv[LATENT_PAIRS];
-            float s = 0.0F, dp = 0.0F;
+            tc_fence_after_sync();
+            uint32_t p_packed[16], ds_packed[16];
+            score_tile_share(p, st_tmem, dpt_tmem, sh->rows[t & 1], group, key_pos, sh->masked[t & 1] != 0, p_packed, ds_packed);
+            tmem_st_x16(st_tmem, p_packed);
+            tmem_st_x16(dpt_tmem, ds_packed);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&sh->p_ready));
+        }
+        if (alive) {
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->final_full), 0, abort_flag, &absorbed_backward_status));
+        }
+        if (alive) {
+            tc_fence_after_sync();
+            const bool valid = key_pos < p.sequence;
+            const size_t key_row = static_cast<size_t>(b) * p.sequence + key_pos;
+            // group g writes dlatent columns 128g..128g+127 of this half and dkey_rope columns 32g..32g+31
+            __nv_bfloat16* dlat_row = p.dlatent + key_row * RANK + half * 256 + group * 128;
 #pragma unroll
-            for (int i = 0; i < PAIRS; ++i) {
-                qv[i] = load_pair(&queries[r][64 * i + 2 * lane]);
-                s += qv[i].x * kv[i].x + qv[i].y * kv[i].y;
+            for (int c = 0; c < 4; ++c) {
+                uint32_t values[32];
+                tmem_ld_x32(tmem_base + lane_base + TMEM_DLAT + group * 128 + c * 32, values);
+                tmem_wait_ld();
+                if (valid) {
+                    store_bf16x32(dlat_row + c * 32, values);
+                }
             }
-#pragma unroll
-            for (int i = 0; i < LATENT_PAIRS; ++i) {
-                gv[i] = load_pair(&gradients[r][64 * i + 2 * lane]);
-                dp += gv[i].x * kv[i].x + gv[i].y * kv[i].y;
+            if (half == 0) {
+                uint32_t values[32];
+                tmem_ld_x32(tmem_base + lane_base + TMEM_DROPE + group * 32, values);
+                tmem_wait_ld();
+                if (valid) {
+                    store_bf16x32(p.dk_rope + key_row * ROPE + group * 32, values);
+                }
             }
-            s = warp_sum(s);
-            dp = warp_sum(dp);
-            const float probability = __expf(s * scale - row_lse[r]);
-            const float ds = probability * (dp - row_delta[r]) * scale;
-#pragma unroll
-            for (int i = 0; i < LATENT_PAIRS; ++i) {
-                // score path plus value path (the latent is both K and V)
-                grad[i].x += ds * qv[i].x + probability * gv[i].x;
-                grad[i].y += ds * qv[i].y + probability * gv[i].y;
-            }
-            grad[LATENT_PAIRS].x += ds * qv[LATENT_PAIRS].x;
-            grad[LATENT_PAIRS].y += ds * qv[LATENT_PAIRS].y;
         }
     }
-    if (active) {
-        const size_t key_row = static_cast<size_t>(b) * sequence + key;
-#pragma unroll
-        for (int i = 0; i < LATENT_PAIRS; ++i) {
-            *reinterpret_cast<__nv_bfloat162*>(dkv_latent + key_row * RANK + 64 * i + 2 * lane) = __float22bfloat162_rn(grad[i]);
+
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag != 0) {
+        for (int k = 0; k < 64; ++k) {
+            __nanosleep(1000);
         }
-        *reinterpret_cast<__nv_bfloat162*>(dk_rope + key_row * ROPE + 2 * lane) = __float22bfloat162_rn(grad[LATENT_PAIRS]);
+    }
+    if (warp == MMA_WARP) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLUMNS);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Query side.  Tensor memory: dQ^T as five 64-column blocks at 0..319 (block m holds output
+// columns 128m..128m+127 on the lanes and the 64 rows on the columns; block 4 is the rotary part
+// on lanes 0..63), S^T 320..383, dP^T 384..447.  Shared memory: the 64 rows' query_latent (8
+// chunks), query_rope (1) and dO (8) as 8 KB K-major chunks, a 16 KB dS^T tile (the MN-major B
+// operand of dQ^T += K^T dS^T), a ring of two 32 KB units (pairs of 16 KB key chunks), constants.
+// Per key tile: 5 units (chunk pairs 0-1 .. 6-7, then the rotary chunk alone) for S^T and dP^T,
+// the softmax, and the same 5 units again as the MN-major A operand of the gradient product.
+// The rotary unit's second half is whatever the slot held before: its products land on lanes
+// 64..127 of block 4, which nothing reads.
+// ---------------------------------------------------------------------------
+namespace qs {
+constexpr int RING_SLOTS = 2;
+constexpr int SLOT_BYTES = 2 * KEY_CHUNK;
+constexpr int Q_BYTES = CHUNKS * ROW_CHUNK;
+constexpr int DO_BYTES = LATENT_CHUNKS * ROW_CHUNK;
+constexpr int DS_BYTES = KEYS * 128;
+constexpr int SMEM_BYTES = Q_BYTES + DO_BYTES + DS_BYTES + RING_SLOTS * SLOT_BYTES + MISC_BYTES + 1024;
+constexpr int UNITS_PER_TILE = 10;
+constexpr uint32_t TMEM_DQT = 0;
+constexpr uint32_t TMEM_X0 = 320;
+constexpr uint32_t TMEM_X1 = 384;
+static_assert(SMEM_BYTES <= 232448, "query-side shared memory");
+
+struct Shared {
+    uint64_t resident_full;
+    uint64_t unit_full[RING_SLOTS];
+    uint64_t unit_empty[RING_SLOTS];
+    uint64_t rows_ready;
+    uint64_t s_ready;
+    uint64_t ds_ready;          // 256 softmax threads: dS^T is in shared memory
+    uint64_t final_full;
+    uint32_t tmem_base;
+    int abort_flag;
+    RowConstants rows;
+};
+static_assert(sizeof(Shared) <= MISC_BYTES, "query-side barrier block too large");
+}  // namespace qs
+
+__global__ void __launch_bounds__(THREADS, 1) absorbed_backward_query_kernel(const __grid_constant__ AbsorbedBackwardParams p) {
+    using namespace qs;
+    extern __shared__ uint8_t smem_raw[];
+    if (*reinterpret_cast<volatile int*>(&absorbed_backward_status) == STATUS_WAIT_TIMEOUT) {
+        return;
+    }
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    const int b = blockIdx.z;
+    const int rows_per_sequence = p.sequence * p.heads;
+    const int row0 = static_cast<int>(gridDim.x - 1 - blockIdx.x) * ROWS;       // late rows see the most keys: longest first
+    const int last_row = min(row0 + ROWS, rows_per_sequence) - 1;
+    const int first_token = row0 / p.heads;
+    const int tile_count = (last_row / p.heads) / KEYS + 1;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023U) & ~1023U;
+    uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t q_smem = smem_base;
+    const uint32_t do_smem = q_smem + Q_BYTES;
+    const uint32_t ds_smem = do_smem + DO_BYTES;
+    uint8_t* ds_ptr = smem_aligned + Q_BYTES + DO_BYTES;
+    const uint32_t ring = ds_smem + DS_BYTES;
+    Shared* sh = reinterpret_cast<Shared*>(smem_aligned + Q_BYTES + DO_BYTES + DS_BYTES + RING_SLOTS * SLOT_BYTES);
+    volatile int* abort_flag = &sh->abort_flag;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&sh->resident_full), 1);
+        for (int i = 0; i < RING_SLOTS; ++i) {
+            mbar_init(smem_u32(&sh->unit_full[i]), 1);
+            mbar_init(smem_u32(&sh->unit_empty[i]), 1);
+        }
+        mbar_init(smem_u32(&sh->rows_ready), 1);
+        mbar_init(smem_u32(&sh->s_ready), 1);
+        mbar_init(smem_u32(&sh->ds_ready), 256);
+        mbar_init(smem_u32(&sh->final_full), 1);
+        sh->abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc(smem_u32(&sh->tmem_base), TMEM_COLUMNS);
+        tmem_relinquish();
+    }
+    if (warp == LOAD_WARP && lane == 0) {
+        tma_prefetch_descriptor(&p.q_lat);
+        tma_prefetch_descriptor(&p.q_rope);
+        tma_prefetch_descriptor(&p.d_out);
+        tma_prefetch_descriptor(&p.k_lat);
+        tma_prefetch_descriptor(&p.k_rope);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&sh->tmem_base);
+
+    if (warp == LOAD_WARP) {
+        // =================== TMA producer ===================================
+        fill_row_constants(p, sh->rows, b, row0, lane);
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(smem_u32(&sh->rows_ready));
+            const uint32_t bar = smem_u32(&sh->resident_full);
+            mbar_arrive_expect_tx(bar, Q_BYTES + DO_BYTES);
+            const int y = b * rows_per_sequence + row0;
+            for (int c = 0; c < LATENT_CHUNKS; ++c) {
+                tma_load_2d(q_smem + c * ROW_CHUNK, &p.q_lat, bar, c * 64, y);
+                tma_load_2d(do_smem + c * ROW_CHUNK, &p.d_out, bar, c * 64, y);
+            }
+            tma_load_2d(q_smem + LATENT_CHUNKS * ROW_CHUNK, &p.q_rope, bar, 0, y);
+            bool alive = true;
+            int unit = 0;
+            for (int j = 0; j < tile_count && alive; ++j) {
+                const int ky = b * p.sequence + j * KEYS;
+                for (int u = 0; u < UNITS_PER_TILE && alive; ++u, ++unit) {
+                    const int slot = unit % RING_SLOTS;
+                    if (unit >= RING_SLOTS) {
+                        alive = mbar_wait(smem_u32(&sh->unit_empty[slot]), (unit / RING_SLOTS - 1) & 1, abort_flag, &absorbed_backward_status);
+                        if (!alive) {
+                            break;
+                        }
+                    }
+                    const uint32_t full = smem_u32(&sh->unit_full[slot]);
+                    const uint32_t dst = ring + slot * SLOT_BYTES;
+                    const int pair = u % 5;
+                    if (pair == 4) {
+                        mbar_arrive_expect_tx(full, KEY_CHUNK);
+                        tma_load_2d(dst, &p.k_rope, full, 0, ky);
+                    } else {
+                        mbar_arrive_expect_tx(full, 2 * KEY_CHUNK);
+                        tma_load_2d(dst, &p.k_lat, full, pair * 128, ky);
+                        tma_load_2d(dst + KEY_CHUNK, &p.k_lat, full, pair * 128 + 64, ky);
+                    }
+                }
+            }
+        }
+    } else if (warp == MMA_WARP) {
+        // =================== MMA issuer (whole warp, elected lane executes) ==
+        const uint32_t leader = elect_one();
+        constexpr uint32_t IDESC_SCORE = make_idesc_bf16(KEYS, ROWS, false, false);
+        constexpr uint32_t IDESC_DQT = make_idesc_bf16(128, ROWS, true, true);        // A = key chunks MN-major, B = dS^T MN-major
+        bool alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->resident_full), 0, abort_flag, &absorbed_backward_status));
+        int unit = 0;
+        auto wait_unit = [&]() -> uint32_t {
+            const int slot = unit % RING_SLOTS;
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->unit_full[slot]), (unit / RING_SLOTS) & 1, abort_flag, &absorbed_backward_status));
+            tc_fence_after_sync();
+            return ring + slot * SLOT_BYTES;
+        };
+        auto release_unit = [&]() {
+            mma_commit_elect(smem_u32(&sh->unit_empty[unit % RING_SLOTS]), leader);
+            ++unit;
+        };
+        for (int j = 0; j < tile_count && alive; ++j) {
+            // ---- S^T = K Q^T, dP^T = latent dO^T ----
+            for (int u = 0; u < 5 && alive; ++u) {
+                const uint32_t src = wait_unit();
+                if (!alive) {
+                    break;
+                }
+                const int chunks_here = u == 4 ? 1 : 2;
+                for (int cc = 0; cc < chunks_here; ++cc) {
+                    const int chunk = 2 * u + cc;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        mma_ss_elect(tmem_base + TMEM_X0, make_kmajor_desc(src + cc * KEY_CHUNK + k * 32), make_kmajor_desc(q_smem + chunk * ROW_CHUNK + k * 32),
+                                     IDESC_SCORE, (chunk | k) != 0 ? 1U : 0U, leader);
+                    }
+                    if (chunk < LATENT_CHUNKS) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            mma_ss_elect(tmem_base + TMEM_X1, make_kmajor_desc(src + cc * KEY_CHUNK + k * 32),
+                                         make_kmajor_desc(do_smem + chunk * ROW_CHUNK + k * 32), IDESC_SCORE, (chunk | k) != 0 ? 1U : 0U, leader);
+                        }
+                    }
+                }
+                release_unit();
+            }
+            if (!alive) {
+                break;
+            }
+            // this commit also covers the gradient products of the previous tile, the last readers of the dS^T tile
+            mma_commit_elect(smem_u32(&sh->s_ready), leader);
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->ds_ready), j & 1, abort_flag, &absorbed_backward_status));
+            if (!alive) {
+                break;
+            }
+            tc_fence_after_sync();
+            // ---- dQ^T block m += (key chunks 2m, 2m+1)^T dS^T ----
+            for (int m = 0; m < 5 && alive; ++m) {
+                const uint32_t src = wait_unit();
+                if (!alive) {
+                    break;
+                }
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    mma_ss_elect(tmem_base + TMEM_DQT + m * ROWS, make_smem_desc(src + k * 2048, KEY_CHUNK, 1024), make_smem_desc(ds_smem + k * 2048, 16, 1024),
+                                 IDESC_DQT, (j | k) != 0 ? 1U : 0U, leader);
+                }
+                release_unit();
+            }
+        }
+        if (alive) {
+            mma_commit_elect(smem_u32(&sh->final_full), leader);
+        }
+    } else {
+        // =================== softmax: thread = (key, 32 of the 64 rows) ======
+        const int group = warp / 4;
+        const int r = threadIdx.x % KEYS;
+        const uint32_t lane_base = static_cast<uint32_t>((warp % 4) * 32) << 16;
+        const uint32_t st_tmem = tmem_base + lane_base + TMEM_X0 + group * 32;
+        const uint32_t dpt_tmem = tmem_base + lane_base + TMEM_X1 + group * 32;
+        const bool ragged = row0 + ROWS > rows_per_sequence;
+        bool alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->rows_ready), 0, abort_flag, &absorbed_backward_status));
+        for (int j = 0; j < tile_count && alive; ++j) {
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->s_ready), j & 1, abort_flag, &absorbed_backward_status));
+            if (!alive) {
+                break;
+            }
+            tc_fence_after_sync();
+            const int key_pos = j * KEYS + r;
+            const bool masked = ragged || j * KEYS + KEYS - 1 > first_token;
+            uint32_t p_packed[16], ds_packed[16];
+            score_tile_share(p, st_tmem, dpt_tmem, sh->rows, group, key_pos, masked, p_packed, ds_packed);
+            // row r of the MN-major tile: 64 rows = eight 16-byte units, swizzled by the key index
+            uint8_t* row = ds_ptr + r * 128;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int unit16 = group * 4 + i;
+                *reinterpret_cast<uint4*>(row + ((unit16 ^ (r & 7)) * 16)) =
+                    make_uint4(ds_packed[4 * i], ds_packed[4 * i + 1], ds_packed[4 * i + 2], ds_packed[4 * i + 3]);
+            }
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&sh->ds_ready));
+        }
+        if (alive) {
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->final_full), 0, abort_flag, &absorbed_backward_status));
+        }
+        if (alive) {
+            tc_fence_after_sync();
+            // thread = output column (lane r of block m), values = rows 32*group .. 32*group+31
+            const size_t first_global_row = static_cast<size_t>(b) * rows_per_sequence + row0 + group * 32;
+            const int rows_here = min(32, rows_per_sequence - (row0 + group * 32));
+#pragma unroll
+            for (int m = 0; m < 5; ++m) {
+                uint32_t values[32];
+                tmem_ld_x32(tmem_base + lane_base + TMEM_DQT + m * ROWS + group * 32, values);
+                tmem_wait_ld();
+                if (m < 4) {
+                    __nv_bfloat16* dst = p.dq_lat + first_global_row * RANK + m * 128 + r;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        if (e < rows_here) {
+                            dst[static_cast<size_t>(e) * RANK] = __float2bfloat16(__uint_as_float(values[e]));
+                        }
+                    }
+                } else if (r < ROPE) {
+                    __nv_bfloat16* dst = p.dq_rope + first_global_row * ROPE + r;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        if (e < rows_here) {
+                            dst[static_cast<size_t>(e) * ROPE] = __float2bfloat16(__uint_as_float(values[e]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag != 0) {
+        for (int k = 0; k < 64; ++k) {
+            __nanosleep(1000);
+        }
+    }
+    if (warp == MMA_WARP) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLUMNS);
+    }
+}
+
+void configure_kernels() {
+    static bool done[16] = {};
+    int device = 0;
+    CUDA_CHECK(cudaGetDevice(&device));
+    if (device < 16 && done[device]) {
+        return;
+    }
+    CUDA_CHECK(cudaFuncSetAttribute(absorbed_backward_key_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ks::SMEM_BYTES));
+    CUDA_CHECK(cudaFuncSetAttribute(absorbed_backward_query_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, qs::SMEM_BYTES));
+    if (device < 16) {
+        done[device] = true;
     }
 }
 
 }  // namespace
 
-void mla_compressed_attention_backward_cuda(__nv_bfloat16* query_latent_gradient, __nv_bfloat16* query_rope_gradient,
-                                            __nv_bfloat16* kv_latent_gradient, __nv_bfloat16* key_rope_gradient,
-                                            const __nv_bfloat16* output_gradient, const __nv_bfloat16* output, const float* logsumexp,
-                                            const __nv_bfloat16* query_latent, const __nv_bfloat16* query_rope,
-                                            const __nv_bfloat16* kv_latent, const __nv_bfloat16* key_rope, int batch_size,
-                                            int sequence_length, int heads, int kv_rank, int rope_size, float scale, cudaStream_t stream) {
+namespace internal {
+
+int absorbed_backward_device_status(bool reset) {
+    int status = 0;
+    CUDA_CHECK(cudaDeviceSynchronize());
+    CUDA_CHECK(cudaMemcpyFromSymbol(&status, absorbed_backward_status, sizeof(int)));
+    if (reset && status != 0) {
+        const int zero = 0;
+        CUDA_CHECK(cudaMemcpyToSymbol(absorbed_backward_status, &zero, sizeof(int)));
+    }
+    return status;
+}
+
+}  // namespace internal
+
+void mla_compressed_attention_backward_cuda(__nv_bfloat16* dquery_latent, __nv_bfloat16* dquery_rope, __nv_bfloat16* dkv_latent,
+                                            __nv_bfloat16* dkey_rope, const __nv_bfloat16* output_gradient, const __nv_bfloat16* output,
+                                            const float* logsumexp, const __nv_bfloat16* query_latent, const __nv_bfloat16* query_rope,
+                                            const __nv_bfloat16* kv_latent, const __nv_bfloat16* key_rope, int batch_size, int sequence_length,
+                                            int heads, int kv_rank, int rope_size, float scale, cudaStream_t stream) {
     // kernels/attention/mla/sm89.cu:20-24 of the reference: same condition, same message.
     if (kv_rank != MLA_KV_RANK || rope_size != MLA_ROPE_SIZE) {
         throw std::invalid_argument("MLA requires C=512 and RoPE=64");
@@ -262,15 +823,17 @@ void mla_compressed_attention_backward_cuda(__nv_bfloat16* query_latent_gradient
     if (batch_size <= 0 || sequence_length <= 0 || heads <= 0) {
         throw std::invalid_argument("MLA backward requires positive batch, sequence length and heads");
     }
-    if (batch_size > 65535 || static_cast<long long>(sequence_length) * heads * batch_size > 0x7fffffffLL) {
+    if (!(scale > 0.0F)) {
+        throw std::invalid_argument("MLA backward requires a positive softmax scale");
+    }
+    const long long rows_per_sequence = static_cast<long long>(sequence_length) * heads;
+    if (rows_per_sequence * batch_size > 0x7fffffffLL || batch_size > 65535) {
         throw std::invalid_argument("MLA backward shape exceeds the supported index range");
     }
-    for (const void* pointer : {static_cast<const void*>(query_latent_gradient), static_cast<const void*>(query_rope_gradient),
-                                static_cast<const void*>(kv_latent_gradient), static_cast<const void*>(key_rope_gradient),
-                                static_cast<const void*>(output_gradient), static_cast<const void*>(output),
-                                static_cast<const void*>(logsumexp), static_cast<const void*>(query_latent),
-                                static_cast<const void*>(query_rope), static_cast<const void*>(kv_latent),
-                                static_cast<const void*>(key_rope)}) {
+    for (const void* pointer : {static_cast<const void*>(dquery_latent), static_cast<const void*>(dquery_rope), static_cast<const void*>(dkv_latent),
+                                static_cast<const void*>(dkey_rope), static_cast<const void*>(output_gradient), static_cast<const void*>(output),
+                                static_cast<const void*>(logsumexp), static_cast<const void*>(query_latent), static_cast<const void*>(query_rope),
+                                static_cast<const void*>(kv_latent), static_cast<const void*>(key_rope)}) {
         if (pointer == nullptr) {
             throw std::invalid_argument("null tensor pointer");
         }
@@ -278,14 +841,35 @@ void mla_compressed_attention_backward_cuda(__nv_bfloat16* query_latent_gradient
             throw std::invalid_argument("tensor pointers must be 16-byte aligned");
         }
     }
-    const int rows = sequence_length * heads;
-    absorbed_backward_query_kernel<<<dim3((rows + WARPS - 1) / WARPS, batch_size), THREADS, 0, stream>>>(
-        query_latent_gradient, query_rope_gradient, output_gradient, output, logsumexp, query_latent, query_rope, kv_latent, key_rope,
-        sequence_length, heads, scale);
+    AbsorbedBackwardParams params{};
+    const std::uint64_t q_rows = static_cast<std::uint64_t>(rows_per_sequence) * batch_size;
+    const std::uint64_t k_rows = static_cast<std::uint64_t>(sequence_length) * batch_size;
+    params.q_lat = make_bf16_tile_map(query_latent, q_rows, RANK, RANK, ROWS);
+    params.q_rope = make_bf16_tile_map(query_rope, q_rows, ROPE, ROPE, ROWS);
+    params.d_out = make_bf16_tile_map(output_gradient, q_rows, RANK, RANK, ROWS);
+    params.k_lat = make_bf16_tile_map(kv_latent, k_rows, RANK, RANK, KEYS);
+    params.k_rope = make_bf16_tile_map(key_rope, k_rows, ROPE, ROPE, KEYS);
+    params.dq_lat = dquery_latent;
+    params.dq_rope = dquery_rope;
+    params.dlatent = dkv_latent;
+    params.dk_rope = dkey_rope;
+    params.lse = logsumexp;
+    params.batch = batch_size;
+    params.sequence = sequence_length;
+    params.heads = heads;
+    params.scale = scale;
+    params.scale_log2 = scale * LOG2E;
+    configure_kernels();
+
+    const std::size_t rows = static_cast<std::size_t>(q_rows);
+    const unsigned delta_blocks = static_cast<unsigned>(rows / 8 + 1 < 148 * 16 ? rows / 8 + 1 : 148 * 16);
+    absorbed_delta_kernel<<<delta_blocks, 256, 0, stream>>>(dquery_rope, output_gradient, output, rows);
     CUDA_CHECK(cudaGetLastError());
-    absorbed_backward_key_kernel<<<dim3((sequence_length + WARPS - 1) / WARPS, batch_size), THREADS, 0, stream>>>(
-        kv_latent_gradient, key_rope_gradient, output_gradient, output, logsumexp, query_latent, query_rope, kv_latent, key_rope,
-        sequence_length, heads, scale);
+    const dim3 key_grid(static_cast<unsigned>((sequence_length + KEYS - 1) / KEYS), 2, batch_size);
+    absorbed_backward_key_kernel<<<key_grid, THREADS, ks::SMEM_BYTES, stream>>>(params);
+    CUDA_CHECK(cudaGetLastError());
+    const dim3 query_grid(static_cast<unsigned>((rows_per_sequence + ROWS - 1) / ROWS), 1, batch_size);
+    absorbed_backward_query_kernel<<<query_grid, THREADS, qs::SMEM_BYTES, stream>>>(params);
     CUDA_CHECK(cudaGetLastError());
 }
 

@@ -38,9 +38,15 @@ void check_prefill_shape(const int* cu_seqlens, int batch_size, int max_sequence
 int mla_device_status(bool reset) {
     const int forward = internal::forward_device_status(reset);
     const int absorbed = internal::absorbed_device_status(reset);
+    const int absorbed_backward = internal::absorbed_backward_device_status(reset);
     const int backward = internal::backward_device_status(reset);
     const int append = internal::append_device_status(reset);
-    return forward != 0 ? forward : (absorbed != 0 ? absorbed : (backward != 0 ? backward : append));
+    for (const int status : {forward, absorbed, absorbed_backward, backward}) {
+        if (status != 0) {
+            return status;
+        }
+    }
+    return append;
 }
 
 }  // namespace dscuda

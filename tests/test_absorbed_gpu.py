@@ -99,7 +99,8 @@ def test_backward_matches_reference_fixture(gpu, name):
         torch.testing.assert_close(got.cpu().float(), g["ag_" + key].float(), atol=1e-2, rtol=1e-2)
 
 
-@pytest.mark.parametrize("b,t,h", [(1, 128, 8), (2, 257, 4), (1, 512, 8), (2, 40, 16)])
+@pytest.mark.parametrize("b,t,h", [(1, 128, 8), (2, 257, 4), (1, 512, 8), (2, 40, 16), (2, 300, 5), (1, 70, 128), (1, 1000, 16), (3, 129, 1),
+                                   (1, 5, 3)])
 def test_backward_matches_oracle(gpu, b, t, h):
     from conftest import rel_l2
     from dscuda_b200 import mla
