@@ -18,13 +18,13 @@
 //      first four bytes of each dquery_rope row (an output the last kernel
 //      overwrites, so no scratch is needed);
 //   2. absorbed_backward_key_kernel: CTA = (128-key tile, one 256-column half of
-//      dlatent).  The key tile (9 chunks, 144 KB) stays in shared memory; every
-//      64-row tile at or after the diagonal streams by twice: its 17 chunks of
-//      query_latent | query_rope | dO for S^T and dP^T = latent dO^T, and after the
-//      softmax the 9 chunks this half needs again, as the B operand of
-//      dlatent += P^T dO + dS^T query_latent and dkey_rope += dS^T query_rope
-//      (P^T and dS^T are bf16 A operands in tensor memory).  Single writer per
-//      output element, no atomics;
+//      dlatent, one part of the rows).  The key tile (9 chunks, 144 KB) stays in
+//      shared memory; the 64-row tiles at or after the diagonal stream by: the 17
+//      chunks of query_latent | query_rope | dO give S^T and dP^T = latent dO^T, and
+//      the 9 chunks this half needs again stay in the ring until after the
+//      softmax, as the B operands of dlatent += dS^T query_latent + P^T dO and
+//      dkey_rope += dS^T query_rope (P^T and dS^T are bf16 A operands in tensor
+//      memory).  Single writer per output element, no atomics;
 //   3. absorbed_backward_query_kernel: CTA = 64 (token, head) rows, resident as the
 //      B operands query_latent | query_rope | dO (136 KB); every 128-key tile up
 //      to the diagonal streams by twice: for S^T / dP^T, and again as the
@@ -39,6 +39,7 @@
 #include "sm100_primitives.cuh"
 #include "../common/tensor_map.h"
 
+#include <algorithm>
 #include <cstddef>
 #include <cstdint>
 #include <stdexcept>
@@ -79,9 +80,26 @@ struct AbsorbedBackwardParams {
     int batch;
     int sequence;
     int heads;
+    int key_chunk;          // key side: at most this many 64-row tiles per CTA
+    int key_direct;         // key side: 1 when every key tile has a single part (results go straight to the outputs)
     float scale;
     float scale_log2;
 };
+
+// Key side work split.  Key tile kt meets the 64-row tiles from floor(kt*128*H/64) to the end of
+// the sequence; that range is cut into ceil(count / key_chunk) parts of equal size, one CTA each,
+// so that the first key tiles (which meet every row) do not set the kernel's duration.  With more
+// than one part the CTAs write fp32 partial sums, part p of key row (b, key) at
+// scratch[((p*B + b)*T + key)*576 ..], and absorbed_backward_reduce_kernel adds them in part
+// order.  The scratch is the dquery_latent output, which the query-side kernel overwrites last.
+__device__ __forceinline__ int key_tile_row_tiles(const AbsorbedBackwardParams& p, int key_tile) {
+    const int rows_per_sequence = p.sequence * p.heads;
+    return (rows_per_sequence + 63) / 64 - static_cast<int>((static_cast<long long>(key_tile) * 128 * p.heads) / 64);
+}
+
+__device__ __forceinline__ int key_tile_parts(const AbsorbedBackwardParams& p, int key_tile) {
+    return (key_tile_row_tiles(p, key_tile) + p.key_chunk - 1) / p.key_chunk;
+}
 
 // Per-row constants of a 64-row tile, written by the load warp, read by every softmax thread.
 struct RowConstants {
@@ -173,6 +191,13 @@ __device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const uint32_t
     }
 }
 
+__device__ __forceinline__ void store_f32x32(float* dst, const uint32_t* values) {
+#pragma unroll
+    for (int e = 0; e < 32; e += 4) {
+        *reinterpret_cast<uint4*>(dst + e) = make_uint4(values[e], values[e + 1], values[e + 2], values[e + 3]);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // delta[row] = sum_c dO[row,c] * O[row,c]; one warp per (token, head) row.  The result is parked
 // in the first four bytes of the row's dquery_rope output.
@@ -209,16 +234,19 @@ __global__ void __launch_bounds__(256) absorbed_delta_kernel(__nv_bfloat16* dq_r
 // Key side.  Tensor memory: dlatent half 0..255, dkey_rope 256..319, S^T 320..383 (P^T overwrites
 // it as bf16), dP^T 384..447 (dS^T likewise).  Shared memory: the key tile (9 x 16 KB), a ring of
 // five 16 KB units, constants.  A unit is one TMA transaction of one or two 8 KB row chunks.
-// Per row tile, in this order: 4 units of query_latent chunk pairs, 1 of query_rope, 4 of dO
-// pairs (S^T and dP^T); then, after the softmax, 2 units of this half's dO pairs, 2 of its
-// query_latent pairs and 1 of query_rope (the gradient products).
+// Per row tile, nine units in this order: the other half's two query_latent pairs and two dO
+// pairs, then this half's two query_latent pairs, query_rope, and this half's two dO pairs.  All
+// nine feed S^T / dP^T; the last five (exactly the ring) are not released after that: they stay
+// where they are and serve as the B operands of the gradient products after the softmax, so a
+// row tile is streamed once (136 KB), and they are released in the order they were loaded.
 // ---------------------------------------------------------------------------
 namespace ks {
 constexpr int RING_SLOTS = 5;
 constexpr int SLOT_BYTES = 2 * ROW_CHUNK;
 constexpr int RESIDENT_BYTES = CHUNKS * KEY_CHUNK;
 constexpr int SMEM_BYTES = RESIDENT_BYTES + RING_SLOTS * SLOT_BYTES + MISC_BYTES + 1024;
-constexpr int UNITS_PER_TILE = 14;
+constexpr int UNITS_PER_TILE = 9;
+constexpr int RETAINED_FROM = 4;          // units 4..8 of a tile are kept for the gradient products
 constexpr uint32_t TMEM_DLAT = 0;
 constexpr uint32_t TMEM_DROPE = 256;
 constexpr uint32_t TMEM_X0 = 320;
@@ -251,10 +279,20 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_backward_key_kernel(const
     const int lane = threadIdx.x % 32;
     const int b = blockIdx.z;
     const int half = blockIdx.y;                         // which 256 columns of dlatent
-    const int key_start = blockIdx.x * KEYS;             // tile 0 meets the most rows: longest first
+    // blockIdx.x counts (key tile, part) pairs, key tile 0 first
+    int key_tile = 0, part = static_cast<int>(blockIdx.x), parts = key_tile_parts(p, 0);
+    while (part >= parts) {
+        part -= parts;
+        ++key_tile;
+        parts = key_tile_parts(p, key_tile);
+    }
+    const int key_start = key_tile * KEYS;
     const int rows_per_sequence = p.sequence * p.heads;
-    const int first_tile = static_cast<int>((static_cast<long long>(key_start) * p.heads) / ROWS);
-    const int tile_count = (rows_per_sequence + ROWS - 1) / ROWS - first_tile;
+    const int tiles_of_key_tile = key_tile_row_tiles(p, key_tile);
+    const int first_tile = (rows_per_sequence + ROWS - 1) / ROWS - tiles_of_key_tile +
+                           static_cast<int>(static_cast<long long>(part) * tiles_of_key_tile / parts);
+    const int tile_count = static_cast<int>(static_cast<long long>(part + 1) * tiles_of_key_tile / parts) -
+                           static_cast<int>(static_cast<long long>(part) * tiles_of_key_tile / parts);
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023U) & ~1023U;
     uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -331,18 +369,16 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_backward_key_kernel(const
                     // which tensor and which chunk pair this unit carries
                     const CUtensorMap* map;
                     int chunk;                           // first chunk; -1: the single rotary chunk
-                    if (u < 4) {
-                        map = &p.q_lat, chunk = 2 * u;
-                    } else if (u == 4) {
+                    if (u < 2) {
+                        map = &p.q_lat, chunk = 4 * (1 - half) + 2 * u;
+                    } else if (u < 4) {
+                        map = &p.d_out, chunk = 4 * (1 - half) + 2 * (u - 2);
+                    } else if (u < 6) {
+                        map = &p.q_lat, chunk = 4 * half + 2 * (u - 4);
+                    } else if (u == 6) {
                         map = &p.q_rope, chunk = -1;
-                    } else if (u < 9) {
-                        map = &p.d_out, chunk = 2 * (u - 5);
-                    } else if (u < 11) {
-                        map = &p.d_out, chunk = 4 * half + 2 * (u - 9);
-                    } else if (u < 13) {
-                        map = &p.q_lat, chunk = 4 * half + 2 * (u - 11);
                     } else {
-                        map = &p.q_rope, chunk = -1;
+                        map = &p.d_out, chunk = 4 * half + 2 * (u - 7);
                     }
                     if (chunk < 0) {
                         mbar_arrive_expect_tx(full, ROW_CHUNK);
@@ -364,37 +400,43 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_backward_key_kernel(const
         constexpr uint32_t IDESC_GRAD = make_idesc_bf16(KEYS, 128, false, true);      // B = two row chunks side by side, MN-major
         constexpr uint32_t IDESC_ROPE = make_idesc_bf16(KEYS, 64, false, true);
         bool alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->resident_full), 0, abort_flag, &absorbed_backward_status));
-        int unit = 0;
-        auto wait_unit = [&]() -> uint32_t {
-            const int slot = unit % RING_SLOTS;
-            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->unit_full[slot]), (unit / RING_SLOTS) & 1, abort_flag, &absorbed_backward_status));
-            tc_fence_after_sync();
-            return ring + slot * SLOT_BYTES;
-        };
-        auto release_unit = [&]() {
-            mma_commit_elect(smem_u32(&sh->unit_empty[unit % RING_SLOTS]), leader);
-            ++unit;
-        };
         for (int t = 0; t < tile_count && alive; ++t) {
+            const int base = t * UNITS_PER_TILE;         // number of the tile's first unit
             // ---- S^T = K Q^T (9 chunks), dP^T = latent dO^T (8 chunks) ----
-            for (int u = 0; u < 9 && alive; ++u) {
-                const uint32_t src = wait_unit();
+            for (int u = 0; u < UNITS_PER_TILE && alive; ++u) {
+                const int slot = (base + u) % RING_SLOTS;
+                alive = __all_sync(0xffffffffU,
+                                   mbar_wait(smem_u32(&sh->unit_full[slot]), ((base + u) / RING_SLOTS) & 1, abort_flag, &absorbed_backward_status));
                 if (!alive) {
                     break;
                 }
-                const bool is_dout = u >= 5;
-                const int first_chunk = u < 4 ? 2 * u : (u == 4 ? LATENT_CHUNKS : 2 * (u - 5));
-                const int chunks_here = u == 4 ? 1 : 2;
+                tc_fence_after_sync();
+                const uint32_t src = ring + slot * SLOT_BYTES;
+                const bool is_dout = (u >= 2 && u < 4) || u >= 7;
+                int first_chunk, chunks_here = 2;
+                if (u < 2) {
+                    first_chunk = 4 * (1 - half) + 2 * u;
+                } else if (u < 4) {
+                    first_chunk = 4 * (1 - half) + 2 * (u - 2);
+                } else if (u < 6) {
+                    first_chunk = 4 * half + 2 * (u - 4);
+                } else if (u == 6) {
+                    first_chunk = LATENT_CHUNKS, chunks_here = 1;
+                } else {
+                    first_chunk = 4 * half + 2 * (u - 7);
+                }
                 const uint32_t acc = tmem_base + (is_dout ? TMEM_X1 : TMEM_X0);
                 for (int cc = 0; cc < chunks_here; ++cc) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        const bool first = (u == 0 || u == 5) && cc == 0 && k == 0;
+                        const bool first = (u == 0 || u == 2) && cc == 0 && k == 0;
                         mma_ss_elect(acc, make_kmajor_desc(k_smem + (first_chunk + cc) * KEY_CHUNK + k * 32),
                                      make_kmajor_desc(src + cc * ROW_CHUNK + k * 32), IDESC_SCORE, first ? 0U : 1U, leader);
                     }
                 }
-                release_unit();
+                if (u < RETAINED_FROM) {
+                    mma_commit_elect(smem_u32(&sh->unit_empty[slot]), leader);
+                }
             }
             if (!alive) {
                 break;
@@ -405,28 +447,29 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_backward_key_kernel(const
                 break;
             }
             tc_fence_after_sync();
-            // ---- dlatent half += P^T dO + dS^T query_latent; dkey_rope += dS^T query_rope ----
-            for (int u = 9; u < UNITS_PER_TILE && alive; ++u) {
-                const uint32_t src = wait_unit();
-                if (!alive) {
-                    break;
-                }
-                if (u < 13) {
-                    const uint32_t operand = tmem_base + (u < 11 ? TMEM_X0 : TMEM_X1);       // P^T for dO, dS^T for query_latent
-                    const uint32_t acc = tmem_base + TMEM_DLAT + ((u - 9) & 1) * 128;
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        mma_ts_elect(acc, operand + (k / 2) * 32 + (k % 2) * 8, make_smem_desc(src + k * 2048, ROW_CHUNK, 1024), IDESC_GRAD,
-                                     (u >= 11 || t != 0 || k != 0) ? 1U : 0U, leader);
-                    }
-                } else {
+            // ---- gradient products on the five retained units, in the order they were loaded:
+            //      dlatent half += dS^T query_latent (2 units), dkey_rope += dS^T query_rope,
+            //      dlatent half += P^T dO (2 units) ----
+            for (int u = RETAINED_FROM; u < UNITS_PER_TILE; ++u) {
+                const int slot = (base + u) % RING_SLOTS;
+                const uint32_t src = ring + slot * SLOT_BYTES;
+                if (u == 6) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         mma_ts_elect(tmem_base + TMEM_DROPE, tmem_base + TMEM_X1 + (k / 2) * 32 + (k % 2) * 8, make_smem_desc(src + k * 2048, ROW_CHUNK, 1024),
                                      IDESC_ROPE, (t | k) != 0 ? 1U : 0U, leader);
                     }
+                } else {
+                    const bool from_dout = u >= 7;
+                    const uint32_t operand = tmem_base + (from_dout ? TMEM_X0 : TMEM_X1);     // P^T for dO, dS^T for query_latent
+                    const uint32_t acc = tmem_base + TMEM_DLAT + ((from_dout ? u - 7 : u - 4) & 1) * 128;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        mma_ts_elect(acc, operand + (k / 2) * 32 + (k % 2) * 8, make_smem_desc(src + k * 2048, ROW_CHUNK, 1024), IDESC_GRAD,
+                                     (from_dout || t != 0 || k != 0) ? 1U : 0U, leader);
+                    }
                 }
-                release_unit();
+                mma_commit_elect(smem_u32(&sh->unit_empty[slot]), leader);
             }
         }
         if (alive) {
@@ -463,23 +506,29 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_backward_key_kernel(const
             tc_fence_after_sync();
             const bool valid = key_pos < p.sequence;
             const size_t key_row = static_cast<size_t>(b) * p.sequence + key_pos;
-            // group g writes dlatent columns 128g..128g+127 of this half and dkey_rope columns 32g..32g+31
+            // group g handles dlatent columns 128g..128g+127 of this half and dkey_rope columns 32g..32g+31
             __nv_bfloat16* dlat_row = p.dlatent + key_row * RANK + half * 256 + group * 128;
+            float* partial_row = reinterpret_cast<float*>(p.dq_lat) +
+                                 ((static_cast<size_t>(part) * p.batch + b) * p.sequence + key_pos) * (RANK + ROPE);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t values[32];
                 tmem_ld_x32(tmem_base + lane_base + TMEM_DLAT + group * 128 + c * 32, values);
                 tmem_wait_ld();
-                if (valid) {
+                if (valid && p.key_direct != 0) {
                     store_bf16x32(dlat_row + c * 32, values);
+                } else if (valid) {
+                    store_f32x32(partial_row + half * 256 + group * 128 + c * 32, values);
                 }
             }
             if (half == 0) {
                 uint32_t values[32];
                 tmem_ld_x32(tmem_base + lane_base + TMEM_DROPE + group * 32, values);
                 tmem_wait_ld();
-                if (valid) {
+                if (valid && p.key_direct != 0) {
                     store_bf16x32(p.dk_rope + key_row * ROPE + group * 32, values);
+                } else if (valid) {
+                    store_f32x32(partial_row + RANK + group * 32, values);
                 }
             }
         }
@@ -496,6 +545,36 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_backward_key_kernel(const
     if (warp == MMA_WARP) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLUMNS);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Adds the key side's fp32 partial sums of one key row, in part order (so the result does not
+// depend on scheduling), and writes bf16 dlatent / dkey_rope.  One CTA of 144 threads per key
+// row, four columns per thread.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(144) absorbed_backward_reduce_kernel(const __grid_constant__ AbsorbedBackwardParams p) {
+    const int key = blockIdx.x;
+    const int b = blockIdx.y;
+    const int parts = key_tile_parts(p, key / KEYS);
+    const float* scratch = reinterpret_cast<const float*>(p.dq_lat);
+    const int column = threadIdx.x * 4;
+    float4 sum = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+    for (int part = 0; part < parts; ++part) {
+        const float4 v = *reinterpret_cast<const float4*>(scratch + ((static_cast<size_t>(part) * p.batch + b) * p.sequence + key) * (RANK + ROPE) + column);
+        sum.x += v.x;
+        sum.y += v.y;
+        sum.z += v.z;
+        sum.w += v.w;
+    }
+    uint2 packed;
+    packed.x = pack_bf16x2(sum.x, sum.y);
+    packed.y = pack_bf16x2(sum.z, sum.w);
+    const size_t key_row = static_cast<size_t>(b) * p.sequence + key;
+    if (column < RANK) {
+        *reinterpret_cast<uint2*>(p.dlatent + key_row * RANK + column) = packed;
+    } else {
+        *reinterpret_cast<uint2*>(p.dk_rope + key_row * ROPE + (column - RANK)) = packed;
     }
 }
 
@@ -780,6 +859,21 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_backward_query_kernel(con
     }
 }
 
+int multiprocessors() {
+    static int cached[64] = {};
+    int device = 0;
+    CUDA_CHECK(cudaGetDevice(&device));
+    if (device >= 0 && device < 64 && cached[device] > 0) {
+        return cached[device];
+    }
+    int count = 0;
+    CUDA_CHECK(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device));
+    if (device >= 0 && device < 64) {
+        cached[device] = count;
+    }
+    return count > 0 ? count : 148;
+}
+
 void configure_kernels() {
     static bool done[16] = {};
     int device = 0;
@@ -865,9 +959,32 @@ void mla_compressed_attention_backward_cuda(__nv_bfloat16* dquery_latent, __nv_b
     const unsigned delta_blocks = static_cast<unsigned>(rows / 8 + 1 < 148 * 16 ? rows / 8 + 1 : 148 * 16);
     absorbed_delta_kernel<<<delta_blocks, 256, 0, stream>>>(dquery_rope, output_gradient, output, rows);
     CUDA_CHECK(cudaGetLastError());
-    const dim3 key_grid(static_cast<unsigned>((sequence_length + KEYS - 1) / KEYS), 2, batch_size);
+    // Key side split (see key_tile_parts): about four waves of CTAs of equal length, never more
+    // parts per key tile than fp32 partial rows fit into the dquery_latent buffer.
+    const int key_tiles = (sequence_length + KEYS - 1) / KEYS;
+    const long long row_tiles = (rows_per_sequence + ROWS - 1) / ROWS;
+    auto tiles_of = [&](int key_tile) { return row_tiles - (static_cast<long long>(key_tile) * KEYS * heads) / ROWS; };
+    long long tile_units = 0;
+    for (int kt = 0; kt < key_tiles; ++kt) {
+        tile_units += tiles_of(kt);
+    }
+    const int sms = multiprocessors();
+    const long long max_parts = std::max<long long>(1, std::min<long long>(64, static_cast<long long>(heads) * RANK * 2 / ((RANK + ROPE) * 4)));
+    long long chunk = std::max<long long>(16, (2 * batch_size * tile_units + 4LL * sms - 1) / (4LL * sms));
+    chunk = std::max(chunk, (row_tiles + max_parts - 1) / max_parts);
+    long long part_count = 0;
+    for (int kt = 0; kt < key_tiles; ++kt) {
+        part_count += (tiles_of(kt) + chunk - 1) / chunk;
+    }
+    params.key_chunk = static_cast<int>(std::min<long long>(chunk, 0x7fffffffLL));
+    params.key_direct = part_count == key_tiles ? 1 : 0;
+    const dim3 key_grid(static_cast<unsigned>(part_count), 2, batch_size);
     absorbed_backward_key_kernel<<<key_grid, THREADS, ks::SMEM_BYTES, stream>>>(params);
     CUDA_CHECK(cudaGetLastError());
+    if (params.key_direct == 0) {
+        absorbed_backward_reduce_kernel<<<dim3(sequence_length, batch_size), 144, 0, stream>>>(params);
+        CUDA_CHECK(cudaGetLastError());
+    }
     const dim3 query_grid(static_cast<unsigned>((rows_per_sequence + ROWS - 1) / ROWS), 1, batch_size);
     absorbed_backward_query_kernel<<<query_grid, THREADS, qs::SMEM_BYTES, stream>>>(params);
     CUDA_CHECK(cudaGetLastError());
