@@ -19,6 +19,13 @@ bytes.  With several GPUs every rank runs the same per-GPU shard (heads are
 independent), there is no collective on the data path, and the job value is the
 sum over ranks divided by the slowest rank's time.
 
+With N > 1 GPUs the job is the head-sharded one: every rank owns its own 128 heads of an
+H = 128*N job (its own draws; the shared rotary key is the same everywhere), the decode
+benchmark's 64 sequences are dealt to the ranks by cache pages, the packed long-context case
+runs 16 heads per GPU, and a small head-sharded problem is gathered over NCCL and compared with
+the CPU oracle on rank 0.  After the timed regions rank 0 also compares slices of the timed
+outputs themselves with the oracle; the line carries the outcome as `verified`.
+
 `--impl reference` times the CPU oracle port of the reference's
 reference/python/mla.py on the host cores, on a bounded sample of the workload.
 """
@@ -43,12 +50,27 @@ from dscuda_b200 import workloads
 from dscuda_b200.workloads import BWD_FLOP_PER_PAIR, FWD_FLOP_PER_PAIR, SCALE, causal_pairs
 
 WORKLOADS = {"train": workloads.CONFIGS["C3"], "prefill": workloads.CONFIGS["C2"]}
-# DRAM bytes (read + written) per (token, head) of the dominant call, from an ncu capture at
-# B=1, S=8192, H=32 (dram__bytes_read.sum + dram__bytes_write.sum): forward kernel 288.2 MB,
-# dQ kernel 382.8 MB, dK/dV kernel 414.6 MB over 262144 (token, head) pairs.  Between S=4096 and
-# S=8192 at H=32 the traffic grew 2.08-2.11x for 2x the pairs, i.e. in proportion; the bench line
-# scales these figures to its own number of pairs.
-DRAM_BYTES_PER_TOKEN_HEAD = {"forward": 288.2e6 / 262144, "backward": (382.8e6 + 414.6e6) / 262144}
+
+
+def dram_traffic(kind: str, token_heads: int):
+    """DRAM bytes (read + written) per launch of the dominant call, from the committed ncu capture
+    summarised in profiles/traffic.json (written by `python -m dscuda_b200.ncu_extract counters ...
+    --traffic-json`): bytes per (token, head) of the reduced-size capture times the (token, head)
+    pairs of this run (the traffic grows in proportion to them).  None when the file has no entry."""
+    path = ROOT / "profiles" / "traffic.json"
+    if not path.exists():
+        return None, None
+    entry = json.loads(path.read_text()).get("train_step")
+    if not entry:
+        return None, None
+    labels = ("prefill_bwd_dq", "prefill_bwd_dkdv") if kind == "backward" else ("prefill_fwd",)
+    try:
+        per_unit = sum(entry["kernels"][label]["dram_bytes_per_token_head"] for label in labels)
+    except KeyError:
+        return None, None
+    return per_unit * token_heads, "profiles/traffic.json (train_step): ncu capture at reduced size, scaled by (token, head) pairs"
+
+
 workload_flops = workloads.dense_flops
 
 
@@ -120,27 +142,117 @@ def time_steps(step, steps, warmup, barrier):
     return start.elapsed_time(stop) / 1e3
 
 
+def bind_to_gpu_numa_node(index):
+    """Keeps this process (and the pinned buffers it allocates afterwards) on the CPU cores of the
+    NUMA node its GPU hangs off.  CPU affinity of this process only; nothing on the GPU changes."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        physical = int(visible.split(",")[index]) if visible and visible.split(",")[index].isdigit() else index
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(physical)).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        bus = bus.lower()
+        if len(bus.split(":")[0]) == 8:                      # NVML pads the domain to eight digits, sysfs uses four
+            bus = bus[4:]
+        node = int(pathlib.Path(f"/sys/bus/pci/devices/{bus}/numa_node").read_text())
+        if node < 0:
+            return {"node": None, "bound": False}
+        cpus = set()
+        for piece in pathlib.Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip().split(","):
+            low, _, high = piece.partition("-")
+            cpus.update(range(int(low), int(high or low) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+        return {"node": node, "bound": bool(allowed), "cpus": len(allowed)}
+    except Exception as error:                                   # evidence, never fatal
+        return {"node": None, "bound": False, "error": repr(error)[:120]}
+
+
+def verify_training(checks, w, x, out, lse, grads):
+    """Slices of the timed step's own outputs against the CPU oracle (oracle/checks.py): batch 0,
+    head 0, the last 256 query rows (O, LSE, dQ) and the first 128 keys (dK_nope, dV); dK_pe (summed
+    over this GPU's heads) on the first 32 keys."""
+    return checks.dense_slices(x, out, lse, grads if w["backward"] else None, SCALE)
+
+
+def verify_sharded(mla, oracle, sharding, rank, world, device):
+    """A small head-sharded problem over NCCL (B=1, S=1024, two heads per rank): every rank computes
+    its own heads, O / LSE / dQ / dK_nope / dV are all-gathered, the fp32 dK_pe partial sums are
+    added, and rank 0 compares the assembled result with the CPU oracle on the unsharded problem."""
+    heads, seq = 2 * world, 1024
+    q_nope, q_pe, k_nope, k_pe, v, dout = oracle.prefill_inputs(11, 1, seq, heads, dout_std=0.1)
+    start, stop = sharding.head_range(heads, world, rank)
+    mine = [t[:, :, start:stop].contiguous().to(device) for t in (q_nope, q_pe, k_nope)] + [k_pe.to(device), v[:, :, start:stop].contiguous().to(device)]
+    out, lse = mla.prefill_forward(*mine, SCALE)
+    workspace = mla.prefill_backward_workspace(1, seq, seq, stop - start, device)
+    grads = mla.prefill_backward(dout[:, :, start:stop].contiguous().to(device), out, lse, *mine, SCALE, workspace=workspace)
+    partial = workspace[: seq * 64 * 4].view(torch.float32).reshape(1, seq, 1, 64).clone()
+    full_out = sharding.gather_heads(out, heads, 2)
+    full_lse = sharding.gather_heads(lse, heads, 1)
+    full = [sharding.gather_heads(grads[i], heads, 2) for i in (0, 1, 3)]
+    dk_pe = sharding.sum_dk_pe_partials(partial)
+    torch.cuda.synchronize()
+    if rank != 0:
+        return None
+    ref_out, ref_lse = oracle.prefill_forward(q_nope, q_pe, k_nope, k_pe, v, SCALE)
+    ref = oracle.prefill_backward(dout, full_out.cpu(), full_lse.cpu(), q_nope, q_pe, k_nope, k_pe, v, SCALE)
+
+    def rel(got, want):
+        return float((got.double().cpu() - want.double()).norm() / want.double().norm())
+
+    return {"out": float((full_out.float().cpu() - ref_out).abs().max()) <= 1e-2 * float(ref_out.abs().max()),
+            "lse": float((full_lse.cpu() - ref_lse).abs().max()) <= 1e-3,
+            "dq": rel(full[0].float(), ref[0]) <= 1e-2, "dk_nope": rel(full[1].float(), ref[1]) <= 1e-2,
+            "dk_pe_sum_over_ranks": rel(dk_pe, ref[2]) <= 1e-2, "dv": rel(full[2].float(), ref[3]) <= 1e-2}
+
+
 def run_ours(args, rank, world, device):
-    from dscuda_b200 import mla
-    from oracle import mla_oracle as oracle  # used by the cpu_baseline leg only
+    from dscuda_b200 import mla, sharding
+    from oracle import checks, mla_oracle as oracle  # checker (verification) and the cpu_baseline leg only
 
     w = dict(WORKLOADS[args.workload])
     for key in ("batch", "seq", "heads"):
         if getattr(args, key) is not None:          # reduced sizes for profiler captures; the line names them
             w[key] = getattr(args, key)
     peaks = measured_peaks()
+    if world > 1:
+        import torch.distributed as dist
+        barrier = dist.barrier
+
+        def reduce_max(values):
+            t = torch.tensor(values, device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return [float(v) for v in t]
+
+        def reduce_sum(values):
+            t = torch.tensor(values, device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+            return [float(v) for v in t]
+    else:
+        def barrier():
+            return None
+
+        def reduce_max(values):
+            return list(values)
+
+        reduce_sum = reduce_max
     if args.only_decode:
-        decode = bench_decode(mla, device, peaks, steps=args.steps, warmup=args.warmup, batch=args.decode_batch)
-        return {"metric": decode["metric"], "value": decode["value"], "unit": decode["unit"], "n_gpus": 1, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": decode["us_per_step"] / 1e3, "higher_is_better": True, "scaling": "weak",
+        decode = bench_decode(mla, checks, sharding, device, peaks, rank, world, barrier, reduce_max, reduce_sum, steps=args.steps,
+                              warmup=args.warmup, batch=args.decode_batch)
+        return {"metric": decode["metric"], "value": decode["value"], "unit": decode["unit"], "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": decode["us_per_step"] / 1e3, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": f"decode only: batch {args.decode_batch}, heads 128, lengths uniform in [1024, 32768], seed 3"},
                 "gpu_launches": 2 * args.steps, "roofline": decode["roofline"], "decode": decode} if rank == 0 else None
-    x = workloads.dense_inputs(w, device)
+    numa = bind_to_gpu_numa_node(device.index)
+    x = workloads.dense_inputs(w, device, shard=rank)
     fwd_in = (x["q_nope"], x["q_pe"], x["k_nope"], x["k_pe"], x["v"])
     out = torch.empty_like(x["v"])
     lse = torch.empty(w["batch"], w["heads"], w["seq"], device=device)
     launches = 1
+    grads = None
     if w["backward"]:
         workspace = mla.prefill_backward_workspace(w["batch"], w["seq"], w["batch"] * w["seq"], w["heads"], device)
         grads = (torch.empty(w["batch"], w["seq"], w["heads"], 192, device=device, dtype=torch.bfloat16),
@@ -158,17 +270,11 @@ def run_ours(args, rank, world, device):
         if w["backward"]:
             backward()
 
-    if world > 1:
-        import torch.distributed as dist
-        barrier = dist.barrier
-    else:
-        def barrier():
-            return None
-
     with ClockSampler(device.index) as sampler:
         seconds = time_steps(step, args.steps, args.warmup, barrier)
     clocks = sampler.summary()
     assert mla.device_status() == 0, "a kernel reported a bounded-wait timeout"
+    verified = {"train_step_slices": verify_training(checks, w, x, out, lse, grads)} if rank == 0 and not args.skip_verify else {}
 
     # dominant call timed alone (same stream, CUDA events) for the roofline object
     dominant = backward if w["backward"] else forward
@@ -183,52 +289,71 @@ def run_ours(args, rank, world, device):
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = result_host.numel() * result_host.element_size()
 
-    def e2e_run(steps):
+    def e2e_run(steps, compute=True):
         pipe = HostPipeline(x, device)
         pipe.stage(host)
         for i in range(steps):
             if i + 1 < steps:
                 pipe.stage(host)
             staged = pipe.acquire()
-            ins = (staged["q_nope"], staged["q_pe"], staged["k_nope"], staged["k_pe"], staged["v"])
-            mla.prefill_forward(*ins, SCALE, output=out, lse=lse)
-            if w["backward"]:
-                mla.prefill_backward(staged["dout"], out, lse, *ins, SCALE, workspace=workspace, grads=grads)
-            result_host.copy_(lse, non_blocking=True)
+            if compute:
+                ins = (staged["q_nope"], staged["q_pe"], staged["k_nope"], staged["k_pe"], staged["v"])
+                mla.prefill_forward(*ins, SCALE, output=out, lse=lse)
+                if w["backward"]:
+                    mla.prefill_backward(staged["dout"], out, lse, *ins, SCALE, workspace=workspace, grads=grads)
+                result_host.copy_(lse, non_blocking=True)
             pipe.release()
 
+    def timed(function, steps):
+        barrier()
+        torch.cuda.synchronize()
+        first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        first.record()
+        function(steps)                              # every copy is enqueued after `first` and finishes before `last`
+        last.record()
+        last.synchronize()
+        barrier()
+        torch.cuda.synchronize()
+        return first.elapsed_time(last) / 1e3
+
     e2e_steps = max(2, min(args.steps, 8))
-    e2e_run(2)                                   # warm-up
-    barrier()
-    torch.cuda.synchronize()
-    e2e_start, e2e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_start.record()
-    e2e_run(e2e_steps)                           # every copy is enqueued after e2e_start and finishes before e2e_stop
-    e2e_stop.record()
-    e2e_stop.synchronize()
-    barrier()
-    torch.cuda.synchronize()
-    e2e_seconds = e2e_start.elapsed_time(e2e_stop) / 1e3
+    e2e_run(2)                                       # warm-up
+    e2e_seconds = timed(e2e_run, e2e_steps)
+    # the host link alone, all ranks at once: the ceiling of any pipeline that feeds every step from the host
+    copy_seconds = timed(lambda steps: e2e_run(steps, compute=False), e2e_steps)
 
     flops = workload_flops(w)
-    times = torch.tensor([seconds, e2e_seconds], device=device, dtype=torch.float64)
-    if world > 1:
-        import torch.distributed as dist
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    seconds, e2e_seconds = float(times[0]), float(times[1])
+    seconds, e2e_seconds, copy_seconds = reduce_max([seconds, e2e_seconds, copy_seconds])
+    del host
 
-    decode = bench_decode(mla, device, peaks) if world == 1 and not args.skip_decode else None
+    prefill = None
+    if w["backward"] and not args.skip_decode:
+        del x, out, lse, grads, workspace
+        torch.cuda.empty_cache()
+        prefill = bench_prefill(mla, checks, device, peaks, rank, barrier, reduce_max, verify=rank == 0 and not args.skip_verify)
+    decode = bench_decode(mla, checks, sharding, device, peaks, rank, world, barrier, reduce_max, reduce_sum) if not args.skip_decode else None
+    varlen = bench_varlen(mla, device, peaks, rank, world, barrier, reduce_max) if not args.skip_decode else None
     append = bench_cache_append(mla, device, peaks) if world == 1 and not args.skip_decode else None
     rope = bench_rope(mla, device, peaks) if world == 1 and not args.skip_decode else None
     absorbed = bench_absorbed(mla, device, peaks) if world == 1 and not args.skip_decode else None
     flash = bench_flash(mla, device, peaks) if world == 1 and not args.skip_decode else None
     cpu = cpu_baseline(oracle, 12.0) if world == 1 and not args.skip_cpu else None
-    varlen = bench_varlen(mla, device, peaks) if world == 1 and not args.skip_decode else None
+    if world > 1 and not args.skip_verify:
+        verified["head_sharded_over_nccl"] = verify_sharded(mla, oracle, sharding, rank, world, device)
+    assert mla.device_status() == 0, "a kernel reported a device-side error status"
 
     if rank != 0:
         return None
+    if decode is not None and "verified" in decode:
+        verified["decode"] = decode.pop("verified")
+    if prefill is not None and "verified" in prefill:
+        verified["prefill"] = prefill.pop("verified")
     value = flops * world * args.steps / seconds / 1e12
     achieved = dominant_flops / dominant_seconds / 1e12
+    traffic, traffic_source = dram_traffic("backward" if w["backward"] else "forward", w["batch"] * w["seq"] * w["heads"])
+    e2e_value = flops * world * e2e_steps / e2e_seconds / 1e12
+    ceiling_value = flops * world * e2e_steps / copy_seconds / 1e12
+    all_checks = [ok for group in verified.values() if group for ok in group.values()]
     line = {
         "metric": "MLA fwd+bwd TFLOP/s (bf16 causal)" if w["backward"] else "MLA prefill fwd TFLOP/s (bf16 causal)",
         "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -236,50 +361,87 @@ def run_ours(args, rank, world, device):
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload}: causal non-absorbed MLA, B={w['batch']} S={w['seq']} H={w['heads']} per GPU, "
                                f"qk=128+64 (shared k_pe), v=128, seed {w['seed']}",
-                   "per_gpu_tflops": value / world, "sharding": "heads x batch per GPU, no collective on the data path",
+                   "per_gpu_tflops": value / world,
+                   "sharding": f"rank r owns heads 128r..128r+127 of the H={128 * world} job (own draws, shared k_pe); no collective on the data path",
                    "l2": "inputs (>= 1.9 GB per step) exceed the 126 MB L2; no flush needed"},
         "clocks": clocks,
-        "e2e": {"value": flops * world * e2e_steps / e2e_seconds / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "h2d_gbs_per_rank": h2d * e2e_steps / e2e_seconds / 1e9,
+                "host_link_ceiling": {"value": ceiling_value, "unit": "TFLOP/s", "h2d_gbs_per_rank": h2d * e2e_steps / copy_seconds / 1e9,
+                                      "how": "the same staged copies with no kernels, all ranks at once"},
+                "fraction_of_ceiling": e2e_value / ceiling_value, "numa": numa},
         "gpu_launches": launches * args.steps,
+        "verified": bool(all_checks) and all(all_checks), "verified_checks": verified,
         "roofline": {"bound": "tensor", "kernel": "prefill backward (dQ + dK/dV kernels)" if w["backward"] else "attention_forward_kernel<3>",
                      "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": achieved / peaks["tensor"],
                      "peak_source": peaks["source"] + " sustained cuBLAS bf16", "frac_of_burst_peak": achieved / peaks["tensor_burst"],
-                     "traffic": DRAM_BYTES_PER_TOKEN_HEAD["backward" if w["backward"] else "forward"] * w["batch"] * w["seq"] * w["heads"],
-                     "traffic_source": "ncu capture at B=1 S=8192 H=32, scaled by (token, head) pairs"},
-        "cpu_baseline": cpu, "decode": decode, "varlen": varlen, "cache_append": append, "rope": rope, "absorbed": absorbed, "flash": flash,
+                     "traffic": traffic, "traffic_source": traffic_source},
+        "cpu_baseline": cpu, "prefill": prefill, "decode": decode, "varlen": varlen, "cache_append": append, "rope": rope, "absorbed": absorbed,
+        "flash": flash,
     }
     return line
 
 
-def bench_decode(mla, device, peaks, steps=20, warmup=3, splits=8, batch=64):
-    """Absorbed paged decode at batch 64, heads 128, lengths uniform in [1024, 32768] (seed 3)."""
+def bench_prefill(mla, checks, device, peaks, rank, barrier, reduce_max, steps=10, warmup=3, verify=True):
+    """Causal forward alone at B=4, S=4096, H=128 per GPU (the prefill configuration)."""
+    w = workloads.CONFIGS["C2"]
+    x = workloads.dense_inputs(w, device, shard=rank)
+    fwd_in = (x["q_nope"], x["q_pe"], x["k_nope"], x["k_pe"], x["v"])
+    out = torch.empty_like(x["v"])
+    lse = torch.empty(w["batch"], w["heads"], w["seq"], device=device)
+    seconds = reduce_max([time_steps(lambda: mla.prefill_forward(*fwd_in, SCALE, output=out, lse=lse), steps, warmup, barrier) / steps])[0]
+    tflops = workloads.dense_flops(w) / seconds / 1e12
+    result = {"metric": "MLA prefill fwd TFLOP/s per GPU (bf16 causal)", "value": tflops, "unit": "TFLOP/s", "ms_per_step": seconds * 1e3,
+              "workload": f"B={w['batch']} S={w['seq']} H={w['heads']} per GPU, seed {w['seed']}", "timing": "slowest rank",
+              "frac_of_measured_sustained_peak": tflops / peaks["tensor"], "frac_of_measured_burst_peak": tflops / peaks["tensor_burst"]}
+    if verify:
+        result["verified"] = verify_training(checks, w, x, out, lse, None)
+    return result
+
+
+def bench_decode(mla, checks, sharding, device, peaks, rank, world, barrier, reduce_max, reduce_sum, steps=20, warmup=3, splits=8, batch=64):
+    """Absorbed paged decode at batch 64, heads 128, lengths uniform in [1024, 32768] (seed 3).  With
+    several GPUs the sequences are dealt to the ranks by cache pages (`sharding.decode_partition`),
+    every cached token is still read by exactly one GPU, and the job's GB/s is all bytes over the
+    slowest rank's time."""
     query, cache, table, lengths = workloads.decode_inputs(seed=3, batch=batch, heads=128)
+    mine = sharding.decode_partition(lengths.tolist(), world)[rank] if world > 1 else list(range(batch))
+    query, table, lengths = query[mine].contiguous(), table[mine].contiguous(), lengths[mine].contiguous()
     total_tokens = int(lengths.sum())
     q, c, t, n = (z.to(device) for z in (query, cache, table, lengths))
-    workspace = mla.decode_workspace(batch, 128, splits, 512, device)
-    out = torch.empty(batch, 1, 128, 512, device=device, dtype=torch.bfloat16)
-    lse = torch.empty(batch, 128, 1, device=device)
+    local = len(mine)
+    workspace = mla.decode_workspace(local, 128, splits, 512, device)
+    out = torch.empty(local, 1, 128, 512, device=device, dtype=torch.bfloat16)
+    lse = torch.empty(local, 128, 1, device=device)
 
     def step():
         mla.mla_decode(q, c, t, n, SCALE, splits=splits, workspace=workspace, output=out, lse=lse)
 
-    seconds = time_steps(step, steps, warmup, lambda: None) / steps
-    algorithmic = workloads.decode_bytes(lengths, table, batch, 128)
+    seconds = reduce_max([time_steps(step, steps, warmup, barrier) / steps])[0]
+    algorithmic = workloads.decode_bytes(lengths, table[:, : int(((lengths + 63) // 64).max())], local, 128)
     flops = workloads.decode_flops(lengths, 128)
-    gbs = algorithmic / seconds / 1e9
-    return {"metric": "absorbed MLA decode HBM GB/s", "value": gbs, "unit": "GB/s", "us_per_step": seconds * 1e6,
-            "tokens": total_tokens, "algorithmic_bytes": algorithmic, "splits": splits, "tflops": flops / seconds / 1e12,
-            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"],
-                         "peak_source": peaks["source"] + " copy bandwidth", "tensor_frac": flops / seconds / 1e12 / peaks["tensor_burst"]}}
+    own_gbs = algorithmic / seconds / 1e9
+    algorithmic_all, flops_all, tokens_all = reduce_sum([algorithmic, flops, total_tokens])
+    gbs = algorithmic_all / seconds / 1e9
+    # the shortest and the longest of this rank's sequences against the oracle
+    torch.cuda.synchronize()
+    order = sorted(range(local), key=lambda i: int(lengths[i]))
+    ok = checks.decode_sequences(query, cache, table, lengths, out, lse, SCALE, sorted({order[0], order[-1]})).values()
+    ok = reduce_sum([0.0 if all(ok) else 1.0])[0] == 0.0
+    return {"metric": "absorbed MLA decode HBM GB/s", "value": gbs, "unit": "GB/s", "us_per_step": seconds * 1e6, "timing": "slowest rank",
+            "tokens": int(tokens_all), "algorithmic_bytes": int(algorithmic_all), "splits": splits, "tflops": flops_all / seconds / 1e12,
+            "sequences_per_gpu": local if world == 1 else "dealt by cache pages", "per_gpu_gbs": gbs / world, "rank0_gbs": own_gbs,
+            "verified": {"shortest_and_longest_sequence_of_every_rank": ok},
+            "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / world / peaks["hbm"],
+                         "peak_source": peaks["source"] + " copy bandwidth", "tensor_frac": flops_all / world / seconds / 1e12 / peaks["tensor_burst"]}}
 
 
-def bench_varlen(mla, device, peaks, heads=16, steps=3, warmup=1):
+def bench_varlen(mla, device, peaks, rank, world, barrier, reduce_max, heads=16, steps=3, warmup=1):
     """Packed long-context forward+backward: the 16 sequence lengths of seed 4 (log-uniform in
-    [512, 32768], 121 320 tokens), 16 heads per GPU (the per-GPU shard of the 128-head job)."""
+    [512, 32768], 121 320 tokens), 16 heads per GPU (each rank its own 16 heads of the 128-head job)."""
     lengths = workloads.varlen_lengths()
     total = sum(lengths)
-    tensors, cu = workloads.packed_inputs(lengths, heads, 4, device)
+    tensors, cu = workloads.packed_inputs(lengths, heads, 4, device, shard=rank)
     x = (tensors["q_nope"], tensors["q_pe"], tensors["k_nope"], tensors["k_pe"], tensors["v"])
     dout = tensors["dout"]
     out = torch.empty_like(x[4])
@@ -291,10 +453,11 @@ def bench_varlen(mla, device, peaks, heads=16, steps=3, warmup=1):
         mla.prefill_forward(*x, SCALE, cu, max(lengths), output=out, lse=lse)
         mla.prefill_backward(dout, out, lse, *x, SCALE, cu, max(lengths), workspace=workspace, grads=grads)
 
-    seconds = time_steps(step, steps, warmup, lambda: None) / steps
+    seconds = reduce_max([time_steps(step, steps, warmup, barrier) / steps])[0]
     tflops = workloads.packed_flops(lengths, heads) / seconds / 1e12
     return {"metric": "packed long-context MLA fwd+bwd TFLOP/s per GPU", "value": tflops, "unit": "TFLOP/s", "ms_per_step": seconds * 1e3,
-            "tokens": total, "sequences": len(lengths), "heads_per_gpu": heads, "frac_of_measured_sustained_peak": tflops / peaks["tensor"]}
+            "timing": "slowest rank", "job_tflops": tflops * world, "tokens": total, "sequences": len(lengths), "heads_per_gpu": heads,
+            "frac_of_measured_sustained_peak": tflops / peaks["tensor"]}
 
 
 def bench_cache_append(mla, device, peaks, batch=64, tokens=4096, steps=20, warmup=3):
@@ -339,7 +502,7 @@ def bench_absorbed(mla, device, peaks, shapes=((1, 512, 8), (4, 2048, 16)), step
         rows.append({"shape": f"B={b} T={t} H={h}", "forward_us": fwd * 1e6, "backward_us": bwd * 1e6,
                      "forward_tflops": pairs * 2 * (576 + 512) / fwd / 1e12,
                      "backward_tflops": pairs * 2 * (576 + 512 + 576 + 576 + 512) / bwd / 1e12})
-    return {"metric": "absorbed MLA causal forward / backward", "kernels": "forward tcgen05; backward CUDA cores", "shapes": rows}
+    return {"metric": "absorbed MLA causal forward / backward", "kernels": "forward and backward tcgen05", "shapes": rows}
 
 
 def bench_flash(mla, device, peaks, batch=4, seq=4096, q_heads=64, kv_heads=8, steps=10, warmup=3):
@@ -442,6 +605,7 @@ def main():
     parser.add_argument("--decode-batch", type=int, default=64)
     parser.add_argument("--skip-decode", action="store_true")
     parser.add_argument("--skip-cpu", action="store_true")
+    parser.add_argument("--skip-verify", action="store_true", help="leave out the oracle checks of the timed outputs (profiler captures)")
     args = parser.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

@@ -54,17 +54,20 @@ def decode_flops(lengths: torch.Tensor, heads: int) -> int:
     return 2 * (576 + 512) * heads * int(lengths.sum())
 
 
-def dense_inputs(config: dict, device: torch.device) -> Dict[str, torch.Tensor]:
+def dense_inputs(config: dict, device: torch.device, shard: int = 0) -> Dict[str, torch.Tensor]:
     """Seeded N(0,1) bf16 tensors drawn on the device.  Rotary embedding is input preparation:
-    the kernels take q_pe / k_pe as they are."""
-    g = torch.Generator(device=device).manual_seed(config["seed"])
+    the kernels take q_pe / k_pe as they are.  `shard` selects the per-head tensors of one head
+    shard of a larger job (a different stream of draws per shard); `k_pe`, the rotary key every head
+    shares, is the same for every shard."""
+    shared = torch.Generator(device=device).manual_seed(config["seed"])
+    g = torch.Generator(device=device).manual_seed(config["seed"] + 7919 * shard) if shard else shared
     b, s, h = config["batch"], config["seq"], config["heads"]
 
-    def draw(*shape, std=1.0):
-        return (torch.randn(*shape, device=device, generator=g, dtype=torch.float32) * std).bfloat16()
+    def draw(*shape, std=1.0, generator=g):
+        return (torch.randn(*shape, device=device, generator=generator, dtype=torch.float32) * std).bfloat16()
 
-    tensors = dict(q_nope=draw(b, s, h, 128), q_pe=draw(b, s, h, 64), k_nope=draw(b, s, h, 128), k_pe=draw(b, s, 1, 64),
-                   v=draw(b, s, h, 128))
+    k_pe = draw(b, s, 1, 64, generator=shared)
+    tensors = dict(q_nope=draw(b, s, h, 128), q_pe=draw(b, s, h, 64), k_nope=draw(b, s, h, 128), k_pe=k_pe, v=draw(b, s, h, 128))
     if config["backward"]:
         tensors["dout"] = draw(b, s, h, 128, std=config["dout_std"])
     return tensors
@@ -77,15 +80,17 @@ def varlen_lengths(seed: int = 4, count: int = 16, low: int = 512, high: int = 3
     return [int(round(math.exp(math.log(low) + float(x) * (math.log(high) - math.log(low))))) for x in u]
 
 
-def packed_inputs(lengths: List[int], heads: int, seed: int, device: torch.device, dout_std: float = 0.1):
-    """Packed [total, H, *] tensors plus int32 cu_seqlens on the device."""
+def packed_inputs(lengths: List[int], heads: int, seed: int, device: torch.device, dout_std: float = 0.1, shard: int = 0):
+    """Packed [total, H, *] tensors plus int32 cu_seqlens on the device (`shard` as in dense_inputs)."""
     total = sum(lengths)
-    g = torch.Generator(device=device).manual_seed(seed)
+    shared = torch.Generator(device=device).manual_seed(seed)
+    g = torch.Generator(device=device).manual_seed(seed + 7919 * shard) if shard else shared
 
-    def draw(*shape, std=1.0):
-        return (torch.randn(*shape, device=device, generator=g, dtype=torch.float32) * std).bfloat16()
+    def draw(*shape, std=1.0, generator=g):
+        return (torch.randn(*shape, device=device, generator=generator, dtype=torch.float32) * std).bfloat16()
 
-    tensors = dict(q_nope=draw(total, heads, 128), q_pe=draw(total, heads, 64), k_nope=draw(total, heads, 128), k_pe=draw(total, 1, 64),
+    k_pe = draw(total, 1, 64, generator=shared)
+    tensors = dict(q_nope=draw(total, heads, 128), q_pe=draw(total, heads, 64), k_nope=draw(total, heads, 128), k_pe=k_pe,
                    v=draw(total, heads, 128))
     tensors["dout"] = draw(total, heads, 128, std=dout_std)
     cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=device)
