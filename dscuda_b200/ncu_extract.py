@@ -48,6 +48,7 @@ KERNEL_PATTERNS = (
     (r"decode_combine_kernel", "decode_combine"),
     (r"absorbed_backward_query_kernel", "absorbed_bwd_query"),
     (r"absorbed_backward_key_kernel", "absorbed_bwd_key"),
+    (r"absorbed_backward_reduce_kernel", "absorbed_bwd_reduce"),
     (r"cache_append_fp8_kernel", "cache_append_fp8"),
     (r"cache_append_kernel", "cache_append"),
     (r"rope_apply_kernel", "rope_apply"),
@@ -176,7 +177,7 @@ def read_counters(text: str) -> List[dict]:
             if field == "time_us":
                 value *= TIME_UNITS_US.get(units[index], 1e-3)
             elif field.endswith("_bytes"):
-                value *= BYTE_UNITS.get(units[index], 1.0)
+                value *= BYTE_UNITS.get(units[index].split("/")[0], 1.0)        # "Kbyte/block" -> "Kbyte"
             entry[field] = value
         result.append(entry)
     return result
