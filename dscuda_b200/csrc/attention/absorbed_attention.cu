@@ -78,14 +78,6 @@ enum Mode : int { MODE_CAUSAL_PREFILL = 0, MODE_PAGED_DECODE = 1 };
 
 __device__ int absorbed_status = 0;
 
-// Scratch for mla_decode_forward_static_cuda: room for STATIC_DECODE_RECORDS
-// split partials of (maximum, sum, 512 outputs).  It lives in the image of the
-// library, so every GPU that loads the library keeps these 16.1 MiB until the
-// process ends.  The name below is only a host-side handle in host code; the
-// device address is looked up once per device with cudaGetSymbolAddress.
-constexpr std::size_t STATIC_DECODE_RECORDS = 8192;
-static __device__ __align__(256) float decode_static_scratch[STATIC_DECODE_RECORDS * (MLA_KV_RANK + 2)];
-
 struct AbsorbedParams {
     CUtensorMap q_lat;      // [rows, 512] box 128 x 64
     CUtensorMap q_rope;     // [rows, 64]  box 128 x 64
@@ -922,131 +914,6 @@ void mla_compressed_attention_forward_cuda(__nv_bfloat16* output, float* logsume
     const dim3 grid(1, static_cast<unsigned>((rows_per_sequence + ROWS - 1) / ROWS * 2), batch_size);
     absorbed_attention_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(params);
     CUDA_CHECK(cudaGetLastError());
-}
-
-std::size_t mla_decode_workspace_elements(int batch_size, int heads, int splits, int kv_rank) {
-    // kernels/attention/mla/sm89.cu:539-541 of the reference.
-    return static_cast<std::size_t>(batch_size) * heads * splits * (kv_rank + 2);
-}
-
-namespace {
-
-// Shared by the decode entry points.  `cache_blocks` <= 0: the number of physical pages is
-// unknown (the reference's interface does not carry it).
-void launch_decode(__nv_bfloat16* output, float* logsumexp, const __nv_bfloat16* query, const __nv_bfloat16* paged_kv_cache,
-                   const int* block_table, const int* cache_lengths, float* workspace, int batch_size, int heads, int kv_rank,
-                   int rope_size, int page_size, int pages_per_sequence, int cache_blocks, int splits, float scale, cudaStream_t stream) {
-    check_absorbed_shape(kv_rank, rope_size);
-    if (batch_size <= 0 || heads <= 0 || pages_per_sequence <= 0 || splits <= 0) {
-        throw std::invalid_argument("MLA decode requires positive batch, heads, pages and splits");
-    }
-    if (page_size <= 0 || page_size % KEYS != 0) {
-        throw std::invalid_argument("MLA decode requires page_size to be a positive multiple of 64");
-    }
-    if (!(scale > 0.0F)) {
-        throw std::invalid_argument("MLA decode requires a positive softmax scale");
-    }
-    if (batch_size > 65535 || splits > 65535 || static_cast<long long>(batch_size) * heads > 0x7fffffffLL ||
-        static_cast<long long>(pages_per_sequence) * page_size > 0x7fffffffLL) {
-        throw std::invalid_argument("MLA decode shape exceeds the supported index range");
-    }
-    check_aligned({output, logsumexp, query, paged_kv_cache, workspace});
-    if (block_table == nullptr || cache_lengths == nullptr) {
-        throw std::invalid_argument("null tensor pointer");
-    }
-    AbsorbedParams params{};
-    const std::uint64_t q_rows = static_cast<std::uint64_t>(batch_size) * heads;
-    // Without a page count the view is given the largest row count a tensor map can hold and
-    // only rows named by the block table are ever touched.  With one, the view ends where the
-    // cache ends and a page number outside it is replaced and reported by the kernel.
-    const std::uint64_t k_rows = cache_blocks > 0 ? static_cast<std::uint64_t>(cache_blocks) * page_size : 1ULL << 31;
-    params.q_lat = make_bf16_tile_map(query, q_rows, RANK, WIDTH, ROWS);
-    params.q_rope = make_bf16_tile_map(query + RANK, q_rows, ROPE, WIDTH, ROWS);
-    params.k_lat = make_bf16_tile_map(paged_kv_cache, k_rows, RANK, WIDTH, KEYS);
-    params.k_rope = make_bf16_tile_map(paged_kv_cache + RANK, k_rows, ROPE, WIDTH, KEYS);
-    params.mode = MODE_PAGED_DECODE;
-    params.batch = batch_size;
-    params.sequence = 1;
-    params.heads = heads;
-    params.block_table = block_table;
-    params.lengths = cache_lengths;
-    params.workspace = workspace;
-    params.page_size = page_size;
-    params.pages = pages_per_sequence;
-    params.splits = splits;
-    params.cache_blocks = cache_blocks > 0 ? cache_blocks : 0;
-    params.scale = scale;
-    params.scale_log2 = scale * 1.4426950408889634F;
-    configure_kernel();
-    // one CTA per SM, in pairs that share a key range (the two halves of the value columns)
-    const int pairs = std::max(1, multiprocessor_count() / 2);
-    const dim3 grid(2 * pairs, 1, 1);
-    absorbed_attention_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(params);
-    CUDA_CHECK(cudaGetLastError());
-    decode_combine_kernel<<<dim3(heads, batch_size), 128, 0, stream>>>(output, logsumexp, workspace, cache_lengths, heads, splits);
-    CUDA_CHECK(cudaGetLastError());
-}
-
-}  // namespace
-
-void mla_decode_forward_cuda(__nv_bfloat16* output, float* logsumexp, const __nv_bfloat16* query, const __nv_bfloat16* paged_kv_cache,
-                             const int* block_table, const int* cache_lengths, float* workspace, int batch_size, int heads, int kv_rank,
-                             int rope_size, int page_size, int pages_per_sequence, int splits, float scale, cudaStream_t stream) {
-    launch_decode(output, logsumexp, query, paged_kv_cache, block_table, cache_lengths, workspace, batch_size, heads, kv_rank, rope_size,
-                  page_size, pages_per_sequence, 0, splits, scale, stream);
-}
-
-void mla_decode_forward_checked_cuda(__nv_bfloat16* output, float* logsumexp, const __nv_bfloat16* query,
-                                     const __nv_bfloat16* paged_kv_cache, const int* block_table, const int* cache_lengths,
-                                     float* workspace, int batch_size, int heads, int kv_rank, int rope_size, int page_size,
-                                     int pages_per_sequence, int cache_blocks, int splits, float scale, cudaStream_t stream) {
-    if (cache_blocks <= 0) {
-        throw std::invalid_argument("checked MLA decode requires the number of cache pages");
-    }
-    launch_decode(output, logsumexp, query, paged_kv_cache, block_table, cache_lengths, workspace, batch_size, heads, kv_rank, rope_size,
-                  page_size, pages_per_sequence, cache_blocks, splits, scale, stream);
-}
-
-std::size_t mla_decode_static_capacity() {
-    return STATIC_DECODE_RECORDS;
-}
-
-void mla_decode_forward_static_cuda(__nv_bfloat16* output, float* logsumexp, const __nv_bfloat16* query,
-                                    const __nv_bfloat16* paged_kv_cache, const int* block_table, const int* cache_lengths, int batch_size,
-                                    int heads, int kv_rank, int rope_size, int page_size, int pages_per_sequence, int splits, float scale,
-                                    cudaStream_t stream) {
-    check_absorbed_shape(kv_rank, rope_size);
-    if (batch_size <= 0 || heads <= 0 || splits <= 0) {
-        throw std::invalid_argument("MLA decode requires positive batch, heads, pages and splits");
-    }
-    const unsigned long long records = static_cast<unsigned long long>(batch_size) * heads * splits;
-    if (records > STATIC_DECODE_RECORDS) {
-        throw std::invalid_argument("static-scratch MLA decode holds at most " + std::to_string(STATIC_DECODE_RECORDS) +
-                                    " split partials (batch*heads*splits = " + std::to_string(records) +
-                                    "); lower splits or use the entry point that takes a workspace");
-    }
-    // Device address of the scratch array, looked up once per device while that
-    // device is current.  The first call on a device does this set-up.
-    constexpr int MAX_DEVICES = 64;
-    static float* scratch_address[MAX_DEVICES] = {};
-    static std::mutex lock;
-    int device = 0;
-    CUDA_CHECK(cudaGetDevice(&device));
-    if (device < 0 || device >= MAX_DEVICES) {
-        throw std::runtime_error("static-scratch MLA decode supports device ordinals below 64");
-    }
-    float* scratch = nullptr;
-    {
-        std::lock_guard<std::mutex> guard(lock);
-        if (scratch_address[device] == nullptr) {
-            void* address = nullptr;
-            CUDA_CHECK(cudaGetSymbolAddress(&address, decode_static_scratch));
-            scratch_address[device] = static_cast<float*>(address);
-        }
-        scratch = scratch_address[device];
-    }
-    mla_decode_forward_cuda(output, logsumexp, query, paged_kv_cache, block_table, cache_lengths, scratch, batch_size, heads, kv_rank,
-                            rope_size, page_size, pages_per_sequence, splits, scale, stream);
 }
 
 }  // namespace dscuda

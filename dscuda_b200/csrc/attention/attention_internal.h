@@ -25,6 +25,7 @@ void launch_prefill_forward(__nv_bfloat16* output, float* logsumexp, const __nv_
 int forward_device_status(bool reset);
 int absorbed_device_status(bool reset);
 int absorbed_backward_device_status(bool reset);
+int decode_device_status(bool reset);
 int backward_device_status(bool reset);
 int append_device_status(bool reset);
 
