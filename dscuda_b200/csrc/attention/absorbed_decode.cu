@@ -82,9 +82,9 @@ constexpr std::size_t STATIC_DECODE_RECORDS = 8192;
 static __device__ __align__(256) float decode_static_scratch[STATIC_DECODE_RECORDS * (MLA_KV_RANK + 2)];
 
 struct DecodeParams {
-    CUtensorMap q_lat;      // [B*H, 512] (row stride 576) box 64 x 64
-    CUtensorMap q_rope;     // [B*H, 64]  box 64 x 64
-    CUtensorMap k_lat;      // [cache rows, 512] (row stride 576) box 64 x 64
+    CUtensorMap q_all;      // [B*H rows][9 chunks][64]: all nine chunks of 64 query rows in one load
+    CUtensorMap k_lat8;     // cache rows as [8 latent chunks][row][64], box of 8 chunks x 64 rows: a stage in one load
+    CUtensorMap k_lat2;     // the same view, box of 2 chunks x 64 rows: one refilled slot pair
     CUtensorMap k_rope;     // [cache rows, 64] box 64 x 64
     const __nv_bfloat16* cache;     // [cache rows, 576]
     const int* block_table; // [B, pages]
@@ -125,7 +125,8 @@ struct Shared {
     uint64_t stage_free[STAGES];    // P V has read the stage
     uint64_t p_free;                // P V has read P (and O is quiescent)
     uint64_t o_final;
-    // leader only: 256 softmax threads (both CTAs) have stored P
+    // leader only: one arrival per softmax warp of either CTA (lane 0, after the warp has synchronised): P is
+    // stored.  One arrival per thread would be 128 serialised transactions on the link between the two SMs.
     uint64_t p_full;
     // 128 softmax threads of this CTA: the two threads of a head have published their maxima / sums
     uint64_t max_ready[2];
@@ -338,7 +339,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
         mbar_init(smem_u32(&sh->rope_free), 1);
         mbar_init(smem_u32(&sh->p_free), 1);
         mbar_init(smem_u32(&sh->o_final), 1);
-        mbar_init(smem_u32(&sh->p_full), 2 * PAIR_HEADS);
+        mbar_init(smem_u32(&sh->p_full), 8);
         mbar_init(smem_u32(&sh->max_ready[0]), PAIR_HEADS);
         mbar_init(smem_u32(&sh->max_ready[1]), PAIR_HEADS);
         mbar_init(smem_u32(&sh->sum_ready), PAIR_HEADS);
@@ -382,9 +383,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
         tmem_relinquish_pair();
     }
     if (warp == LOAD_WARP && lane == 0) {
-        tma_prefetch_descriptor(&p.q_lat);
-        tma_prefetch_descriptor(&p.q_rope);
-        tma_prefetch_descriptor(&p.k_lat);
+        tma_prefetch_descriptor(&p.q_all);
+        tma_prefetch_descriptor(&p.k_lat8);
+        tma_prefetch_descriptor(&p.k_lat2);
         tma_prefetch_descriptor(&p.k_rope);
     }
     tc_fence_before_sync();
@@ -426,10 +427,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
                 if (alive) {
                     const uint32_t bar = smem_u32(&sh->q_full);
                     mbar_arrive_expect_tx(bar, Q_BYTES);
-                    for (int c = 0; c < LATENT_CHUNKS; ++c) {
-                        tma_load_2d(q_smem + c * CHUNK, &p.q_lat, bar, c * 64, q_row0);
-                    }
-                    tma_load_2d(q_smem + LATENT_CHUNKS * CHUNK, &p.q_rope, bar, 0, q_row0);
+                    tma_load_3d(q_smem, &p.q_all, bar, 0, q_row0, 0);
                 }
             }
             alive = __shfl_sync(0xffffffffU, alive ? 1 : 0, 0) != 0;
@@ -471,16 +469,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
             while (alive && (next_a < tile_count || next_r < tile_count || next_b < tile_count)) {
                 int action = 0;
                 if (lane == 0) {
-                    if (next_b < tile_count && next_b < next_a) {
-                        const int tile = tile_index + next_b;
-                        if (mbar_test_wait(smem_u32(&sh->refill_free[tile % STAGES]), (tile / STAGES) & 1)) {
-                            action = 3;
-                        }
-                    }
-                    if (action == 0 && next_r < tile_count) {
+                    if (next_r < tile_count) {
                         const int tile = tile_index + next_r;
                         if (tile == 0 || mbar_test_wait(smem_u32(&sh->rope_free), (tile - 1) & 1)) {
                             action = 2;
+                        }
+                    }
+                    if (action == 0 && next_b < tile_count && next_b < next_a) {
+                        const int tile = tile_index + next_b;
+                        if (mbar_test_wait(smem_u32(&sh->refill_free[tile % STAGES]), (tile / STAGES) & 1)) {
+                            action = 3;
                         }
                     }
                     if (action == 0 && next_a < tile_count) {
@@ -505,9 +503,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
                     if (lane == 0) {
                         const uint32_t bar = smem_u32(&sh->full_a[stage]);
                         mbar_arrive_expect_tx(bar, STAGE_BYTES);
-                        for (int c = 0; c < LATENT_CHUNKS; ++c) {
-                            tma_load_2d(stage_smem + stage * STAGE_BYTES + c * CHUNK, &p.k_lat, bar, c * 64, row);
-                        }
+                        tma_load_3d(stage_smem + stage * STAGE_BYTES, &p.k_lat8, bar, 0, row, 0);
                     }
                     ++next_a;
                     prefetch_up_to(next_a + PREFETCH_TILES);
@@ -527,12 +523,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
                         const uint32_t bar = smem_u32(&sh->full_b[stage]);
                         mbar_arrive_expect_tx(bar, 4 * CHUNK);
                         for (int a = 0; a < 2; ++a) {
-                            for (int i = 0; i < 2; ++i) {
-                                // the other CTA's keys, this CTA's value columns -> one of the slots only S needed
-                                const int chunk = 4 * a + 2 * static_cast<int>(rank) + i;
-                                const int slot = 4 * a + 2 * static_cast<int>(peer) + i;
-                                tma_load_2d(stage_smem + stage * STAGE_BYTES + slot * CHUNK, &p.k_lat, bar, chunk * 64, row);
-                            }
+                            // the other CTA's keys, this CTA's value columns -> the two adjacent slots only S needed
+                            const int chunk = 4 * a + 2 * static_cast<int>(rank);
+                            const int slot = 4 * a + 2 * static_cast<int>(peer);
+                            tma_load_3d(stage_smem + stage * STAGE_BYTES + slot * CHUNK, &p.k_lat2, bar, 0, row, chunk);
                         }
                     }
                     ++next_b;
@@ -546,32 +540,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
         }
     } else if (warp == MMA_WARP && rank != 0) {
         // =================== relay: this CTA's "loaded" events -> the leader =========
-        // Each landed load of this CTA is forwarded as one arrival on the leader's matching barrier, in
-        // whatever order the loads land (per kind they land in tile order).
-        bool alive = true;
-        const uint32_t leader_q = map_to_cta(smem_u32(&sh->peer_q_full), 0);
-        const uint32_t leader_r = map_to_cta(smem_u32(&sh->peer_full_r), 0);
-        const uint32_t leader_a[STAGES] = {map_to_cta(smem_u32(&sh->peer_full_a[0]), 0), map_to_cta(smem_u32(&sh->peer_full_a[1]), 0)};
-        const uint32_t leader_b[STAGES] = {map_to_cta(smem_u32(&sh->peer_full_b[0]), 0), map_to_cta(smem_u32(&sh->peer_full_b[1]), 0)};
-        while (alive && next_segment(p, schedule, walker, seg, cluster, clusters)) {
-            const int tile_count = seg.tile_end - seg.tile_begin;
-            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->q_full), segment_index & 1, abort_flag, &decode_status));
-            if (alive && lane == 0) {
-                mbar_arrive_remote(leader_q);
-            }
-            int next_a = 0, next_r = 0, next_b = 0;
-            long long idle_since = clock64();
-            while (alive && (next_a < tile_count || next_r < tile_count || next_b < tile_count)) {
-                bool progress = false;
-                if (lane == 0) {
-                    if (next_a < tile_count) {
-                        const int tile = tile_index + next_a;
-                        if (mbar_test_wait(smem_u32(&sh->full_a[tile % STAGES]), (tile / STAGES) & 1)) {
-                            mbar_arrive_remote(leader_a[tile % STAGES]);
-                            ++next_a;
-                            progress = true;
-                        }
-                    }
+        // One thread: each landed load of this CTA is forwarded as one arrival on the leader's matching
+        // barrier, in whatever order the loads land (per kind they land in tile order).
+        if (lane == 0) {
+            bool alive = true;
+            const uint32_t leader_q = map_to_cta(smem_u32(&sh->peer_q_full), 0);
+            const uint32_t leader_r = map_to_cta(smem_u32(&sh->peer_full_r), 0);
+            const uint32_t leader_a0 = map_to_cta(smem_u32(&sh->peer_full_a[0]), 0);
+            const uint32_t leader_b0 = map_to_cta(smem_u32(&sh->peer_full_b[0]), 0);
+            static_assert(STAGES == 2, "the relay addresses the two stage barriers as base + 8 * stage");
+            while (alive && next_segment(p, schedule, walker, seg, cluster, clusters)) {
+                const int tile_count = seg.tile_end - seg.tile_begin;
+                alive = mbar_wait(smem_u32(&sh->q_full), segment_index & 1, abort_flag, &decode_status);
+                if (alive) {
+                    mbar_arrive_remote(leader_q);
+                }
+                int next_a = 0, next_r = 0, next_b = 0;
+                long long idle_since = clock64();
+                while (alive && (next_a < tile_count || next_r < tile_count || next_b < tile_count)) {
+                    bool progress = false;
                     if (next_r < tile_count) {
                         const int tile = tile_index + next_r;
                         if (mbar_test_wait(smem_u32(&sh->full_r), tile & 1)) {
@@ -580,10 +567,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
                             progress = true;
                         }
                     }
+                    if (next_a < tile_count) {
+                        const int tile = tile_index + next_a;
+                        if (mbar_test_wait(smem_u32(&sh->full_a[tile % STAGES]), (tile / STAGES) & 1)) {
+                            mbar_arrive_remote(leader_a0 + 8 * (tile % STAGES));
+                            ++next_a;
+                            progress = true;
+                        }
+                    }
                     if (next_b < tile_count) {
                         const int tile = tile_index + next_b;
                         if (mbar_test_wait(smem_u32(&sh->full_b[tile % STAGES]), (tile / STAGES) & 1)) {
-                            mbar_arrive_remote(leader_b[tile % STAGES]);
+                            mbar_arrive_remote(leader_b0 + 8 * (tile % STAGES));
                             ++next_b;
                             progress = true;
                         }
@@ -593,21 +588,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
                     } else if (*abort_flag != 0 || clock64() - idle_since > WAIT_LIMIT_CYCLES) {
                         *abort_flag = 1;
                         atomicExch(&decode_status, STATUS_WAIT_TIMEOUT);
-                        next_a = -1;
+                        alive = false;
                     }
                 }
-                next_a = __shfl_sync(0xffffffffU, next_a, 0);
-                next_r = __shfl_sync(0xffffffffU, next_r, 0);
-                next_b = __shfl_sync(0xffffffffU, next_b, 0);
-                if (next_a < 0) {
-                    alive = false;
-                }
+                tile_index += tile_count;
+                segment_index += 1;
             }
-            tile_index += tile_count;
-            segment_index += 1;
         }
     } else if (warp == MMA_WARP) {
         // =================== MMA issuer (leader CTA) ============================
+        // Lane 0 watches the barriers and picks what to issue; the whole warp then runs the issue code
+        // (uniform control flow) and the elected lane executes the tcgen05 instructions.
         const uint32_t leader = elect_one();
         constexpr uint32_t IDESC_QK = make_idesc_bf16(PAIR_HEADS, TILE_KEYS, false, false);
         constexpr uint32_t IDESC_PV = make_idesc_bf16(PAIR_HEADS, 256, false, true);
@@ -620,21 +611,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
             commit_pair(smem_u32(bar), leader);
             commit_pair(map_to_cta(smem_u32(bar), 1), leader);
         };
-        auto wait2 = [&](uint64_t* own, uint64_t* from_peer, uint32_t parity) {
-            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(own), parity, abort_flag, &decode_status) &&
-                                                mbar_wait(smem_u32(from_peer), parity, abort_flag, &decode_status));
+        // own keys and rotary chunk of `tile` have landed in both CTAs
+        auto s_ready = [&](int tile) -> bool {
+            const int stage = tile % STAGES;
+            const uint32_t parity = (tile / STAGES) & 1;
+            return mbar_test_wait(smem_u32(&sh->full_a[stage]), parity) && mbar_test_wait(smem_u32(&sh->peer_full_a[stage]), parity) &&
+                   mbar_test_wait(smem_u32(&sh->full_r), tile & 1) && mbar_test_wait(smem_u32(&sh->peer_full_r), tile & 1);
+        };
+        // P of `tile` is stored and the refilled slots have landed, in both CTAs
+        auto pv_ready = [&](int tile) -> bool {
+            const int stage = tile % STAGES;
+            const uint32_t parity = (tile / STAGES) & 1;
+            return mbar_test_wait(smem_u32(&sh->p_full), tile & 1) && mbar_test_wait(smem_u32(&sh->full_b[stage]), parity) &&
+                   mbar_test_wait(smem_u32(&sh->peer_full_b[stage]), parity);
         };
         auto issue_s = [&](int tile) {
             const int stage = tile % STAGES;
-            wait2(&sh->full_a[stage], &sh->peer_full_a[stage], (tile / STAGES) & 1);
-            if (!alive) {
-                return;
-            }
-            tc_fence_after_sync();
             const uint32_t s_tmem = tmem_base + TMEM_S + (tile & 1) * HALF_KEYS;
             const uint32_t stage_lo = smem_desc_lo(stage_smem + stage * STAGE_BYTES, 16);
-            // slots {2,3,6,7}: S-only in the leader; then {0,1,4,5}: S-only in the other CTA; then the rotary chunk
-            bool first = true;
+            // The rotary chunk first: there is one slot for it, and the next tile's chunk can only be loaded once
+            // these four MMAs have read it.  Then slots {2,3,6,7} (S-only in the leader), then {0,1,4,5} (S-only in
+            // the other CTA); each group's commit lets that CTA refill the slots.
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                mma_pair_ss_split(s_tmem, q_lo + LATENT_CHUNKS * (CHUNK >> 4) + 2 * k, HI, rope_lo + 2 * k, HI, IDESC_QK, k != 0 ? 1U : 0U, leader);
+            }
+            both(&sh->rope_free);
 #pragma unroll
             for (int group = 0; group < 2; ++group) {
 #pragma unroll
@@ -642,9 +644,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
                     const int c = (group == 0 ? 2 : 0) + (n & 1) + (n >> 1) * 4;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        mma_pair_ss_split(s_tmem, q_lo + c * (CHUNK >> 4) + 2 * k, HI, stage_lo + c * (CHUNK >> 4) + 2 * k, HI, IDESC_QK, first ? 0U : 1U,
-                                          leader);
-                        first = false;
+                        mma_pair_ss_split(s_tmem, q_lo + c * (CHUNK >> 4) + 2 * k, HI, stage_lo + c * (CHUNK >> 4) + 2 * k, HI, IDESC_QK, 1U, leader);
                     }
                 }
                 if (group == 0) {
@@ -653,84 +653,62 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
                     commit_pair(map_to_cta(smem_u32(&sh->refill_free[stage]), 1), leader);
                 }
             }
-            wait2(&sh->full_r, &sh->peer_full_r, tile & 1);
-            if (!alive) {
-                return;
-            }
-            tc_fence_after_sync();
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                mma_pair_ss_split(s_tmem, q_lo + LATENT_CHUNKS * (CHUNK >> 4) + 2 * k, HI, rope_lo + 2 * k, HI, IDESC_QK, 1U, leader);
-            }
-            both(&sh->rope_free);
             both(&sh->s_full[tile & 1]);
+        };
+        auto issue_pv = [&](int tile, bool first_of_segment, bool last_of_segment) {
+            const int stage = tile % STAGES;
+            const uint32_t v_lo = smem_desc_lo(stage_smem + stage * STAGE_BYTES, CHUNK);      // MN-major: the two 64-column chunks are CHUNK apart
+#pragma unroll
+            for (int a = 0; a < 2; ++a) {
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const int g = kk >> 2;          // which 64 keys of the tile
+                    mma_pair_ss_split(tmem_base + TMEM_O + a * 128, p_lo + g * (CHUNK >> 4) + 2 * (kk & 3), HI,
+                                      v_lo + (4 * a + 2 * g) * (CHUNK >> 4) + (kk & 3) * (2048 >> 4), HI, IDESC_PV, (first_of_segment && kk == 0) ? 0U : 1U,
+                                      leader);
+                }
+            }
+            both(&sh->stage_free[stage]);
+            both(&sh->p_free);
+            if (last_of_segment) {
+                both(&sh->o_final);
+            }
         };
         while (alive && next_segment(p, schedule, walker, seg, cluster, clusters)) {
             const int tile_count = seg.tile_end - seg.tile_begin;
-            wait2(&sh->q_full, &sh->peer_q_full, segment_index & 1);
-            if (alive) {
-                issue_s(tile_index);
-            }
-            for (int j = 0; j < tile_count && alive; ++j) {
-                const int tile = tile_index + j;
-                const int stage = tile % STAGES;
-                // Two things are owed now: S of the next tile (runs while this tile's softmax is computed) and
-                // P V of this tile.  Whichever has its inputs first is issued first: waiting for the next tile's
-                // cache rows must not hold back a P V whose P is already there, and the other way round.
-                bool s_owed = j + 1 < tile_count;
-                bool pv_owed = true;
-                const long long start = clock64();
-                while (alive && (s_owed || pv_owed)) {
-                    if (s_owed) {
-                        const int next_stage = (tile + 1) % STAGES;
-                        const uint32_t parity = ((tile + 1) / STAGES) & 1;
-                        const bool ready = mbar_test_wait(smem_u32(&sh->full_a[next_stage]), parity) &&
-                                           mbar_test_wait(smem_u32(&sh->peer_full_a[next_stage]), parity);
-                        if (__all_sync(0xffffffffU, ready) || !pv_owed) {
-                            issue_s(tile + 1);
-                            s_owed = false;
-                            continue;
-                        }
-                    }
-                    if (pv_owed) {
-                        const uint32_t parity = (tile / STAGES) & 1;
-                        const bool ready = mbar_test_wait(smem_u32(&sh->p_full), tile & 1) && mbar_test_wait(smem_u32(&sh->full_b[stage]), parity) &&
-                                           mbar_test_wait(smem_u32(&sh->peer_full_b[stage]), parity);
-                        if (__all_sync(0xffffffffU, ready) || !s_owed) {
-                            // ---- O (+)= P V ----
-                            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->p_full), tile & 1, abort_flag, &decode_status));
-                            if (alive) {
-                                wait2(&sh->full_b[stage], &sh->peer_full_b[stage], parity);
-                            }
-                            if (!alive) {
-                                break;
-                            }
-                            tc_fence_after_sync();
-                            const uint32_t v_lo = smem_desc_lo(stage_smem + stage * STAGE_BYTES, CHUNK);      // MN-major: the two 64-column chunks are CHUNK apart
-#pragma unroll
-                            for (int a = 0; a < 2; ++a) {
-#pragma unroll
-                                for (int kk = 0; kk < 8; ++kk) {
-                                    const int g = kk >> 2;          // which 64 keys of the tile
-                                    mma_pair_ss_split(tmem_base + TMEM_O + a * 128, p_lo + g * (CHUNK >> 4) + 2 * (kk & 3), HI,
-                                                      v_lo + (4 * a + 2 * g) * (CHUNK >> 4) + (kk & 3) * (2048 >> 4), HI, IDESC_PV, (j | kk) != 0 ? 1U : 0U,
-                                                      leader);
-                                }
-                            }
-                            both(&sh->stage_free[stage]);
-                            both(&sh->p_free);
-                            if (j + 1 == tile_count) {
-                                both(&sh->o_final);
-                            }
-                            pv_owed = false;
-                            continue;
-                        }
-                    }
-                    if (__any_sync(0xffffffffU, *abort_flag != 0 || clock64() - start > WAIT_LIMIT_CYCLES)) {
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->q_full), segment_index & 1, abort_flag, &decode_status) &&
+                                                mbar_wait(smem_u32(&sh->peer_q_full), segment_index & 1, abort_flag, &decode_status));
+            // Owed at any time: S of the next tile not yet issued (it runs while the softmax of the tile before
+            // it is computed) and P V of the oldest tile not yet done.  Whichever has its inputs first goes
+            // first: waiting for cache rows must not hold back a P V whose P is there, and the other way round.
+            int next_s = 0, next_pv = 0;
+            long long idle_since = clock64();
+            while (alive && next_pv < tile_count) {
+                int action = 0;
+                if (lane == 0) {
+                    if (next_s < tile_count && next_s <= next_pv + 1 && s_ready(tile_index + next_s)) {
+                        action = 1;
+                    } else if (next_pv < next_s && pv_ready(tile_index + next_pv)) {
+                        action = 2;
+                    } else if (*abort_flag != 0 || clock64() - idle_since > WAIT_LIMIT_CYCLES) {
                         *abort_flag = 1;
                         atomicExch(&decode_status, STATUS_WAIT_TIMEOUT);
-                        alive = false;
+                        action = -1;
                     }
+                }
+                action = __shfl_sync(0xffffffffU, action, 0);
+                if (action < 0) {
+                    alive = false;
+                } else if (action == 1) {
+                    tc_fence_after_sync();
+                    issue_s(tile_index + next_s);
+                    ++next_s;
+                    idle_since = clock64();
+                } else if (action == 2) {
+                    tc_fence_after_sync();
+                    issue_pv(tile_index + next_pv, next_pv == 0, next_pv + 1 == tile_count);
+                    ++next_pv;
+                    idle_since = clock64();
                 }
             }
             tile_index += tile_count;
@@ -872,10 +850,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
                 }
                 fence_proxy_async_smem();
                 tc_fence_before_sync();
-                if (rank == 0) {
-                    mbar_arrive(p_full_bar);
-                } else {
-                    mbar_arrive_remote(p_full_bar);
+                __syncwarp();
+                if (lane == 0) {
+                    if (rank == 0) {
+                        mbar_arrive(p_full_bar);
+                    } else {
+                        mbar_arrive_remote(p_full_bar);
+                    }
                 }
             }
 
@@ -924,7 +905,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
                 }
             }
             // O may be overwritten by the next segment only after every lane has been read out: the next
-            // segment's first P V waits for all 256 P arrivals, which come after this point.
+            // segment's first P V waits for the P arrivals of every softmax thread, which come after this point.
             tc_fence_before_sync();
             tile_index += tile_count;
             segment_index += 1;
@@ -1066,9 +1047,9 @@ void launch_decode(__nv_bfloat16* output, float* logsumexp, const __nv_bfloat16*
     // only rows named by the block table are ever touched.  With one, the view ends where the
     // cache ends and a page number outside it is replaced and reported by the kernel.
     const std::uint64_t k_rows = cache_blocks > 0 ? static_cast<std::uint64_t>(cache_blocks) * page_size : 1ULL << 31;
-    params.q_lat = make_bf16_tile_map(query, q_rows, RANK, WIDTH, CTA_HEADS);
-    params.q_rope = make_bf16_tile_map(query + RANK, q_rows, ROPE, WIDTH, CTA_HEADS);
-    params.k_lat = make_bf16_tile_map(paged_kv_cache, k_rows, RANK, WIDTH, HALF_KEYS);
+    params.q_all = make_bf16_chunked_map(query, q_rows, 9, WIDTH, CTA_HEADS, 9);
+    params.k_lat8 = make_bf16_chunked_map(paged_kv_cache, k_rows, LATENT_CHUNKS, WIDTH, HALF_KEYS, LATENT_CHUNKS);
+    params.k_lat2 = make_bf16_chunked_map(paged_kv_cache, k_rows, LATENT_CHUNKS, WIDTH, HALF_KEYS, 2);
     params.k_rope = make_bf16_tile_map(paged_kv_cache + RANK, k_rows, ROPE, WIDTH, HALF_KEYS);
     params.cache = paged_kv_cache;
     params.block_table = block_table;

@@ -154,6 +154,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* tenso
         : "memory");
 }
 
+// 3-D form: coordinates {x (element), y (row), z (chunk)}.
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void* tensor_map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_dst), "l"(tensor_map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_descriptor(const void* tensor_map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
 }

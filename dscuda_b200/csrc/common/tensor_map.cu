@@ -53,4 +53,27 @@ CUtensorMap make_bf16_tile_map(const void* base, std::uint64_t rows, std::uint64
     return map;
 }
 
+CUtensorMap make_bf16_chunked_map(const void* base, std::uint64_t rows, std::uint32_t chunks, std::uint64_t row_stride_elements,
+                                  std::uint32_t box_rows, std::uint32_t box_chunks) {
+    if ((reinterpret_cast<std::uintptr_t>(base) & 15U) != 0 || (row_stride_elements * 2) % 16 != 0) {
+        throw std::invalid_argument("tensor base and row stride must be 16-byte aligned");
+    }
+    if (rows == 0 || chunks == 0 || box_rows == 0 || box_rows > 256 || box_chunks == 0 || box_chunks > chunks) {
+        throw std::invalid_argument("empty tensor or bad tile shape");
+    }
+    CUtensorMap map;
+    const cuuint64_t dims[3] = {64, rows, chunks};
+    const cuuint64_t strides[2] = {row_stride_elements * 2, 128};
+    const cuuint32_t box[3] = {64, box_rows, box_chunks};
+    const cuuint32_t element_strides[3] = {1, 1, 1};
+    const CUresult result = encode_entry_point()(
+        &map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, element_strides,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (result != CUDA_SUCCESS) {
+        throw std::runtime_error("cuTensorMapEncodeTiled (chunked view) failed with code " + std::to_string(static_cast<int>(result)));
+    }
+    return map;
+}
+
 }  // namespace dscuda

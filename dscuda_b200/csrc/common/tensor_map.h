@@ -16,4 +16,11 @@ namespace dscuda {
 CUtensorMap make_bf16_tile_map(const void* base, std::uint64_t rows, std::uint64_t cols, std::uint64_t row_stride_elements,
                                std::uint32_t box_rows);
 
+// The same rows seen as [chunk][row][64 elements]: `chunks` consecutive 64-column chunks of a row are
+// 128 bytes apart, rows `row_stride_elements` apart.  One load of a box {64, box_rows, box_chunks} at
+// coordinates {0, row, chunk} lands in shared memory chunk after chunk, each a [box_rows x 128 byte]
+// swizzled tile, i.e. what `box_chunks` loads through the 2-D view would have produced.
+CUtensorMap make_bf16_chunked_map(const void* base, std::uint64_t rows, std::uint32_t chunks, std::uint64_t row_stride_elements,
+                                  std::uint32_t box_rows, std::uint32_t box_chunks);
+
 }  // namespace dscuda
