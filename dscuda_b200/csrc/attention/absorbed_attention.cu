@@ -1,16 +1,7 @@
-// Absorbed-latent MLA on sm_100a: every head shares one compressed key/value
-// row of 576 bf16 (512 latent + 64 rotary); the latent part is also the value.
-// One kernel serves two entry points:
-//
-//   * causal prefill forward (mla_compressed_attention_forward_cuda): the 128
-//     rows of a tile are consecutive (token, head) pairs of one sequence and
-//     each row sees keys 0..its token;
-//   * paged split-KV decode (mla_decode_forward_cuda): the 128 rows are the
-//     heads of one sequence's single query token, keys come from 64-token tiles
-//     of the paged cache found through the block table, and each piece of work
-//     writes an unnormalised partial (max, sum, output) that a second kernel
-//     merges.  The decode grid is persistent: one CTA per SM, in pairs, and the
-//     key tiles of all sequences are dealt to the pairs in equal ranges.
+// Causal absorbed-latent MLA forward on sm_100a (mla_compressed_attention_forward_cuda): every
+// head shares one compressed key/value row of 576 bf16 (512 latent + 64 rotary); the latent part is
+// also the value.  The 128 rows of a tile are consecutive (token, head) pairs of one sequence and each
+// row sees keys 0..its token.
 //
 // A 128x512 fp32 output tile would fill all of tensor memory, so a tile is
 // handled by two CTAs: both compute S = Q K^T (K = 576) and each accumulates
@@ -24,7 +15,7 @@
 //
 // Warps 0-3: softmax / epilogue (one thread per row); warp 4: MMA issue (the
 // whole warp runs the loop, one elected lane executes the instruction); warp 5:
-// TMA loads.  All waits are bounded.
+// TMA loads.  All waits are bounded.  (The paged decode lives in absorbed_decode.cu.)
 #include "mla.h"
 #include "cuda_common.h"
 #include "attention_internal.h"
@@ -74,8 +65,6 @@ constexpr float RESCALE_THRESHOLD = 8.0F;
 static_assert(Q_TMEM_CHUNKS * Q_CHUNK_BYTES <= B_RING_BYTES, "Q staging must fit in the value ring");
 static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 
-enum Mode : int { MODE_CAUSAL_PREFILL = 0, MODE_PAGED_DECODE = 1 };
-
 __device__ int absorbed_status = 0;
 
 struct AbsorbedParams {
@@ -83,28 +72,13 @@ struct AbsorbedParams {
     CUtensorMap q_rope;     // [rows, 64]  box 128 x 64
     CUtensorMap k_lat;      // [rows, 512] box 64 x 64
     CUtensorMap k_rope;     // [rows, 64]  box 64 x 64
-    int mode;
     int batch;
-    int sequence;           // prefill: T
+    int sequence;           // T
     int heads;
-    __nv_bfloat16* out;     // prefill: [B,T,H,512]
-    float* lse;             // prefill: [B,H,T]
-    const int* block_table; // decode: [B, pages]
-    const int* lengths;     // decode: [B]
-    float* workspace;       // decode: [B,H,splits,2+512]
-    int page_size;
-    int pages;
-    int splits;
-    int cache_blocks;       // decode: physical pages in the cache, or 0 when the caller did not say
+    __nv_bfloat16* out;     // [B,T,H,512]
+    float* lse;             // [B,H,T]
     float scale;
     float scale_log2;
-};
-
-struct Schedule {
-    int chunk;          // 64-key tiles per CTA pair (range scheme)
-    int total;          // tiles of all units
-    int first_unit;     // first unit that overlaps this pair's range
-    int first_offset;   // global tile index at which that unit starts
 };
 
 struct AbsorbedBarriers {
@@ -120,102 +94,35 @@ struct AbsorbedBarriers {
     uint64_t o_final;           // one phase per segment: the last P V has finished
     uint32_t tmem_base;
     int abort_flag;
-    Schedule schedule;
 };
 static_assert(sizeof(AbsorbedBarriers) <= MISC_BYTES, "barrier block too large");
 
-// One piece of work: tiles [tile_begin, tile_end) of the keys visible to the 128
-// rows `row_tile` of sequence `b`.
+// The work of one CTA: key tiles [0, tile_end) for the 128 rows `row_tile` of sequence `b`.
 struct Segment {
     int b;
     int row_tile;
     int tile_begin;
     int tile_end;
-    int slot;            // decode: which partial record of (b, head) this segment fills
-    bool last_of_unit;   // decode: the segment that reaches the end of the sequence
 };
 
-// Walks the segments of this CTA.  Every role thread runs its own walker over the
-// same schedule, so all roles see the same sequence of segments.
-//
-// Decode units are (sequence, 128-head tile) pairs, laid end to end as one long
-// list of 64-key tiles.  With splits > 1 the list is cut into equal ranges, one
-// per CTA pair, so every pair streams about the same number of cache bytes
-// whatever the sequence lengths are; a unit cut by a range boundary produces one
-// partial per range it touches.  The range length is never smaller than
-// ceil(longest unit / (splits - 1)), which bounds the partials of a unit by
-// `splits`.  With splits == 1 whole units are dealt round-robin.
 struct Walker {
-    int unit;
-    int offset;     // global tile index where `unit` starts
     bool done;
 };
 
-// Cached tokens of sequence `b` the kernel will read: the caller's length, held inside
-// [0, capacity of the sequence's block-table row].
-__device__ __forceinline__ int sequence_length(const AbsorbedParams& p, int b) {
-    return max(0, min(p.lengths[b], p.pages * p.page_size));
-}
-
-__device__ __forceinline__ int unit_tiles(const AbsorbedParams& p, int unit, int head_tiles) {
-    return (sequence_length(p, unit / head_tiles) + KEYS - 1) / KEYS;
-}
-
-__device__ __forceinline__ bool next_segment(const AbsorbedParams& p, const Schedule& s, Walker& w, Segment& seg, int pair, int pairs) {
+// Every role thread calls this in a loop; a CTA has exactly one segment.
+__device__ __forceinline__ bool next_segment(const AbsorbedParams& p, Walker& w, Segment& seg) {
     if (w.done) {
         return false;
     }
-    if (p.mode == MODE_CAUSAL_PREFILL) {
-        const int rows_total = p.sequence * p.heads;
-        const int first = (blockIdx.y >> 1) * ROWS;
-        const int last_token = (min(first + ROWS, rows_total) - 1) / p.heads;
-        seg.b = blockIdx.z;
-        seg.row_tile = blockIdx.y >> 1;
-        seg.tile_begin = 0;
-        seg.tile_end = last_token / KEYS + 1;
-        seg.slot = 0;
-        seg.last_of_unit = true;
-        w.done = true;
-        return true;
-    }
-    const int head_tiles = (p.heads + ROWS - 1) / ROWS;
-    const int units = p.batch * head_tiles;
-    if (p.splits == 1) {
-        if (w.unit >= units) {
-            w.done = true;
-            return false;
-        }
-        seg.b = w.unit / head_tiles;
-        seg.row_tile = w.unit % head_tiles;
-        seg.tile_begin = 0;
-        seg.tile_end = unit_tiles(p, w.unit, head_tiles);
-        seg.slot = 0;
-        seg.last_of_unit = true;
-        w.unit += pairs;
-        return true;
-    }
-    const long long lo = static_cast<long long>(pair) * s.chunk;
-    const long long hi = min(lo + s.chunk, static_cast<long long>(s.total));
-    while (w.unit < units && w.offset < hi) {
-        const int tiles = unit_tiles(p, w.unit, head_tiles);
-        const int begin = static_cast<int>(max(lo, static_cast<long long>(w.offset)) - w.offset);
-        const int end = static_cast<int>(min(hi, static_cast<long long>(w.offset) + tiles) - w.offset);
-        const int unit = w.unit;
-        const int offset = w.offset;
-        w.unit += 1;
-        w.offset += tiles;
-        if (end > begin) {
-            seg.b = unit / head_tiles;
-            seg.row_tile = unit % head_tiles;
-            seg.tile_begin = begin;
-            seg.tile_end = end;
-            seg.slot = pair - offset / s.chunk;
-            seg.last_of_unit = end == tiles;
-            return true;
-        }
-    }
+    const int rows_total = p.sequence * p.heads;
+    const int first = (blockIdx.y >> 1) * ROWS;
+    const int last_token = (min(first + ROWS, rows_total) - 1) / p.heads;
+    seg.b = blockIdx.z;
+    seg.row_tile = blockIdx.y >> 1;
+    seg.tile_begin = 0;
+    seg.tile_end = last_token / KEYS + 1;
     w.done = true;
-    return false;
+    return true;
 }
 
 __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __grid_constant__ AbsorbedParams p) {
@@ -225,11 +132,8 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
     }
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
-    // prefill: grid (1, 2*row_tiles, B); decode: grid (2*pairs, 1, 1)
-    const bool decode = p.mode == MODE_PAGED_DECODE;
-    const int half = decode ? (blockIdx.x & 1) : (blockIdx.y & 1);      // which 256 value columns
-    const int pair = decode ? (blockIdx.x >> 1) : 0;
-    const int pairs = decode ? (gridDim.x >> 1) : 1;
+    // grid (1, 2*row_tiles, B)
+    const int half = blockIdx.y & 1;      // which 256 value columns
 
     // ---- shared memory ------------------------------------------------------
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023U) & ~1023U;
@@ -260,38 +164,6 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
         mbar_init(smem_u32(&bars->o_final), 1);
         bars->abort_flag = 0;
         mbar_init_fence();
-        // ---- schedule of this pair (decode with splits > 1) -------------------
-        Schedule schedule = {1, 0, 0, 0};
-        if (decode && p.splits > 1) {
-            const int head_tiles = (p.heads + ROWS - 1) / ROWS;
-            long long total = 0;
-            int longest = 0;
-            for (int b = 0; b < p.batch; ++b) {
-                const int tiles = (sequence_length(p, b) + KEYS - 1) / KEYS;
-                total += static_cast<long long>(tiles) * head_tiles;
-                longest = max(longest, tiles);
-            }
-            long long chunk = (total + pairs - 1) / pairs;
-            chunk = max(chunk, static_cast<long long>((longest + p.splits - 2) / (p.splits - 1)));
-            chunk = max(chunk, 1LL);
-            schedule.chunk = static_cast<int>(min(chunk, 0x7fffffffLL));
-            schedule.total = static_cast<int>(min(total, 0x7fffffffLL));
-            const long long lo = static_cast<long long>(pair) * schedule.chunk;
-            int unit = 0;
-            long long offset = 0;
-            const int units = p.batch * head_tiles;
-            while (unit < units) {
-                const int tiles = unit_tiles(p, unit, head_tiles);
-                if (offset + tiles > lo) {
-                    break;
-                }
-                offset += tiles;
-                ++unit;
-            }
-            schedule.first_unit = unit;
-            schedule.first_offset = static_cast<int>(offset);
-        }
-        bars->schedule = schedule;
     }
     if (warp == MMA_WARP) {
         tmem_alloc(smem_u32(&bars->tmem_base), TMEM_COLUMNS);
@@ -307,7 +179,6 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
-    const Schedule schedule = bars->schedule;
 
     // Key chunk c holds columns 64c..64c+63 (c = 8: the rotary columns).  Chunks
     // v_first..v_first+3 are this CTA's V (the "B" group); the matching four Q chunks
@@ -319,8 +190,6 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
     auto a_chunk = [&](int i) -> int { return half == 0 ? 4 + i : (i < 4 ? i : 8); };
 
     Walker walker;
-    walker.unit = (decode && p.splits == 1) ? pair : schedule.first_unit;
-    walker.offset = schedule.first_offset;
     walker.done = false;
     Segment seg;
     int segment_index = 0;      // segments this CTA has started (every role counts the same)
@@ -328,12 +197,11 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
 
     if (warp == LOAD_WARP) {
         // =================== TMA producer ===================================
-        // All 32 lanes walk the loop (they prefetch block-table entries, one tile
-        // per lane); lane 0 waits on barriers and issues the loads.
+        // All 32 lanes walk the loop; lane 0 waits on barriers and issues the loads.
         bool alive = true;
-        while (alive && next_segment(p, schedule, walker, seg, pair, pairs)) {
+        while (alive && next_segment(p, walker, seg)) {
             const int tile_count = seg.tile_end - seg.tile_begin;
-            const int q_row0 = decode ? seg.b * p.heads + seg.row_tile * ROWS : seg.b * p.sequence * p.heads + seg.row_tile * ROWS;
+            const int q_row0 = seg.b * p.sequence * p.heads + seg.row_tile * ROWS;
             const uint32_t seg_parity = segment_index & 1;
             if (lane == 0) {
                 // Q is staged through the value ring and (three chunks) kept in shared
@@ -363,25 +231,11 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                 }
             }
             alive = __shfl_sync(0xffffffffU, alive ? 1 : 0, 0) != 0;
-            int table_entry = 0;
             for (int j = 0; j < tile_count && alive; ++j) {
                 const int token = (seg.tile_begin + j) * KEYS;
-                if (decode && (j & 31) == 0) {
-                    // one block-table entry per lane for the next 32 tiles
-                    const int ahead = token + lane * KEYS;
-                    table_entry = ahead < seg.tile_end * KEYS
-                                      ? __ldg(p.block_table + static_cast<size_t>(seg.b) * p.pages + ahead / p.page_size)
-                                      : 0;
-                    if (p.cache_blocks > 0 && static_cast<unsigned>(table_entry) >= static_cast<unsigned>(p.cache_blocks)) {
-                        // a page number outside the cache: read page 0 instead and report it
-                        atomicExch(&absorbed_status, STATUS_BAD_INDEX);
-                        table_entry = 0;
-                    }
-                }
-                const int physical_page = __shfl_sync(0xffffffffU, table_entry, j & 31);
                 if (lane == 0) {
                     const int tile = tile_index + j;
-                    const int y = decode ? physical_page * p.page_size + token % p.page_size : seg.b * p.sequence + token;
+                    const int y = seg.b * p.sequence + token;
                     // "A" group: free once the S of two tiles ago has been computed
                     const int slot_a = tile % A_SLOTS;
                     if (tile >= A_SLOTS) {
@@ -473,7 +327,7 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                 }
                 mma_commit_elect(smem_u32(&bars->s_full[tile & 1]), leader);
             };
-            while (alive && next_segment(p, schedule, walker, seg, pair, pairs)) {
+            while (alive && next_segment(p, walker, seg)) {
                 const int tile_count = seg.tile_end - seg.tile_begin;
                 const uint32_t seg_parity = segment_index & 1;
                 alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->q_full), seg_parity, abort_flag, &absorbed_status) &&
@@ -526,19 +380,14 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
         const uint32_t o_tmem = tmem_base + lane_base + TMEM_O;
         bool alive = true;
 
-        while (alive && next_segment(p, schedule, walker, seg, pair, pairs)) {
+        while (alive && next_segment(p, walker, seg)) {
             const int tile_count = seg.tile_end - seg.tile_begin;
             const uint32_t seg_parity = segment_index & 1;
             int valid_rows;      // rows of the tile that exist
             int kv_end;          // keys >= kv_end are never visible in this segment
             int min_limit;       // smallest per-row key limit; tiles past it need masking
             int limit;           // this row sees keys < limit
-            if (decode) {
-                valid_rows = min(ROWS, p.heads - seg.row_tile * ROWS);
-                kv_end = min(sequence_length(p, seg.b), seg.tile_end * KEYS);
-                min_limit = kv_end;
-                limit = kv_end;
-            } else {
+            {
                 const int rows_total = p.sequence * p.heads;
                 const int first = seg.row_tile * ROWS;
                 valid_rows = min(ROWS, rows_total - first);
@@ -594,8 +443,8 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                     }
                 }
                 if (token0 + KEYS > kv_end) {
-                    // Keys past the end may hold anything (the cache page is only
-                    // partly written); zero them so that 0 * V stays 0 in P V.
+                    // Keys past the end of the tile's visible range belong to the next sequence or lie
+                    // outside the tensor; zero their rows so that 0 * V stays 0 in P V.
                     uint8_t* v_rows = b_ring_ptr + (tile % B_SLOTS) * B_UNIT_BYTES;
                     const int first_bad = kv_end - token0;               // 1..63
                     const int bad_units = (KEYS - first_bad) * 8 * 4;    // 16-byte units in 4 chunks
@@ -679,7 +528,7 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
             }
             tc_fence_after_sync();
             const bool valid = r < valid_rows;
-            if (!decode) {
+            {
                 const int row = seg.row_tile * ROWS + r;                 // (token, head) index inside the sequence
                 const float inverse = 1.0F / l_sum;
                 __nv_bfloat16* out_row = p.out + (static_cast<size_t>(seg.b) * p.sequence * p.heads + row) * RANK + half * HALF_V;
@@ -705,39 +554,6 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
                     const int head = row % p.heads;
                     p.lse[(static_cast<size_t>(seg.b) * p.heads + head) * p.sequence + token] = m_ref * p.scale + logf(l_sum);
                 }
-            } else {
-                const int head = seg.row_tile * ROWS + (valid ? r : 0);
-                float* records = p.workspace + (static_cast<size_t>(seg.b) * p.heads + head) * p.splits * (RANK + 2);
-                float* record = records + static_cast<size_t>(seg.slot) * (RANK + 2);
-                // Each CTA of the pair normalises its own 256 columns with its own (maximum, sum):
-                // the two keep separate running maxima (their score chunks are summed in
-                // different orders), so only a normalised partial is independent of which
-                // maximum a CTA happened to hold.  The record then carries the partial's
-                // log-sum-exp and a sum of 1.
-                const float inverse = 1.0F / l_sum;
-                if (valid && half == 0) {
-                    record[0] = m_ref * p.scale + logf(l_sum);
-                    record[1] = 1.0F;
-                    if (seg.last_of_unit && seg.slot + 1 < p.splits) {
-                        // a sequence fills slots 0..slot in order; the first unused one ends the list
-                        // for the combine kernel (its row sum is 0)
-                        records[static_cast<size_t>(seg.slot + 1) * (RANK + 2)] = -INFINITY;
-                        records[static_cast<size_t>(seg.slot + 1) * (RANK + 2) + 1] = 0.0F;
-                    }
-                }
-#pragma unroll
-                for (int c = 0; c < HALF_V / 32; ++c) {
-                    uint32_t o[32];
-                    tmem_ld_x32(o_tmem + c * 32, o);
-                    tmem_wait_ld();
-                    if (valid) {
-                        float2* dst = reinterpret_cast<float2*>(record + 2 + half * HALF_V + c * 32);
-#pragma unroll
-                        for (int e = 0; e < 32; e += 2) {
-                            dst[e / 2] = make_float2(__uint_as_float(o[e]) * inverse, __uint_as_float(o[e + 1]) * inverse);
-                        }
-                    }
-                }
             }
             // the accumulator and the Q columns in tensor memory may be overwritten by
             // the next segment only after every row has been read out
@@ -762,57 +578,6 @@ __global__ void __launch_bounds__(THREADS, 1) absorbed_attention_kernel(const __
     }
 }
 
-// Merges the split partials of one (sequence, head).  A record is (log-sum-exp of the
-// partial, 1, normalised output); the partials are weighted by exp(lse_s - max lse).
-// Writes bf16 output and the natural-log LSE.  A sequence without cached tokens has no
-// partial at all: its output is NaN and its LSE -inf, what the softmax of an empty row
-// gives in the reference (reference/python/mla.py:36-38).
-__global__ void __launch_bounds__(128) decode_combine_kernel(__nv_bfloat16* output, float* logsumexp, const float* workspace,
-                                                             const int* lengths, int heads, int splits) {
-    const int row = blockIdx.y * heads + blockIdx.x;
-    if (lengths[blockIdx.y] <= 0) {
-        const uint32_t nan2 = 0x7fc07fc0U;
-        *reinterpret_cast<uint2*>(output + static_cast<size_t>(row) * RANK + threadIdx.x * 4) = make_uint2(nan2, nan2);
-        if (threadIdx.x == 0) {
-            logsumexp[row] = -INFINITY;
-        }
-        return;
-    }
-    const float* records = workspace + static_cast<size_t>(row) * splits * (RANK + 2);
-    // Slots are filled in order from 0; the first one with a zero row sum ends the list.
-    float maximum = -INFINITY;
-    int used = 0;
-    for (; used < splits; ++used) {
-        const float l = records[static_cast<size_t>(used) * (RANK + 2) + 1];
-        if (!(l > 0.0F)) {
-            break;
-        }
-        maximum = fmaxf(maximum, records[static_cast<size_t>(used) * (RANK + 2)]);
-    }
-    float normalizer = 0.0F;
-    float acc[4] = {0.0F, 0.0F, 0.0F, 0.0F};
-    const int column = threadIdx.x * 4;
-    for (int s = 0; s < used; ++s) {
-        const float* record = records + static_cast<size_t>(s) * (RANK + 2);
-        const float weight = __expf(record[0] - maximum);
-        normalizer += weight * record[1];
-        const float2 lo = *reinterpret_cast<const float2*>(record + 2 + column);
-        const float2 hi = *reinterpret_cast<const float2*>(record + 4 + column);
-        acc[0] += weight * lo.x;
-        acc[1] += weight * lo.y;
-        acc[2] += weight * hi.x;
-        acc[3] += weight * hi.y;
-    }
-    const float inverse = 1.0F / normalizer;
-    uint2 packed;
-    packed.x = pack_bf16x2(acc[0] * inverse, acc[1] * inverse);
-    packed.y = pack_bf16x2(acc[2] * inverse, acc[3] * inverse);
-    *reinterpret_cast<uint2*>(output + static_cast<size_t>(row) * RANK + column) = packed;
-    if (threadIdx.x == 0) {
-        logsumexp[row] = maximum + logf(normalizer);
-    }
-}
-
 void configure_kernel() {
     static bool done[16] = {};
     int device = 0;
@@ -824,21 +589,6 @@ void configure_kernel() {
     if (device < 16) {
         done[device] = true;
     }
-}
-
-int multiprocessor_count() {
-    static int cached[64] = {};
-    int device = 0;
-    CUDA_CHECK(cudaGetDevice(&device));
-    if (device >= 0 && device < 64 && cached[device] > 0) {
-        return cached[device];
-    }
-    int count = 0;
-    CUDA_CHECK(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device));
-    if (device >= 0 && device < 64) {
-        cached[device] = count;
-    }
-    return count;
 }
 
 void check_absorbed_shape(int kv_rank, int rope_size) {
@@ -900,14 +650,11 @@ void mla_compressed_attention_forward_cuda(__nv_bfloat16* output, float* logsume
     params.q_rope = make_bf16_tile_map(query_rope, q_rows, ROPE, ROPE, ROWS);
     params.k_lat = make_bf16_tile_map(kv_latent, k_rows, RANK, RANK, KEYS);
     params.k_rope = make_bf16_tile_map(key_rope, k_rows, ROPE, ROPE, KEYS);
-    params.mode = MODE_CAUSAL_PREFILL;
     params.batch = batch_size;
     params.sequence = sequence_length;
     params.heads = heads;
     params.out = output;
     params.lse = logsumexp;
-    params.splits = 1;
-    params.page_size = KEYS;
     params.scale = scale;
     params.scale_log2 = scale * 1.4426950408889634F;
     configure_kernel();
