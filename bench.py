@@ -335,6 +335,7 @@ def run_ours(args, rank, world, device):
     varlen = bench_varlen(mla, device, peaks, rank, world, barrier, reduce_max) if not args.skip_decode else None
     append = bench_cache_append(mla, device, peaks) if world == 1 and not args.skip_decode else None
     rope = bench_rope(mla, device, peaks) if world == 1 and not args.skip_decode else None
+    projection = bench_projection(mla, device, peaks) if world == 1 and not args.skip_decode else None
     absorbed = bench_absorbed(mla, device, peaks) if world == 1 and not args.skip_decode else None
     flash = bench_flash(mla, device, peaks) if world == 1 and not args.skip_decode else None
     cpu = cpu_baseline(oracle, 12.0) if world == 1 and not args.skip_cpu else None
@@ -376,8 +377,8 @@ def run_ours(args, rank, world, device):
                      "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": achieved / peaks["tensor"],
                      "peak_source": peaks["source"] + " sustained cuBLAS bf16", "frac_of_burst_peak": achieved / peaks["tensor_burst"],
                      "traffic": traffic, "traffic_source": traffic_source},
-        "cpu_baseline": cpu, "prefill": prefill, "decode": decode, "varlen": varlen, "cache_append": append, "rope": rope, "absorbed": absorbed,
-        "flash": flash,
+        "cpu_baseline": cpu, "prefill": prefill, "decode": decode, "varlen": varlen, "cache_append": append, "rope": rope, "projection": projection,
+        "absorbed": absorbed, "flash": flash,
     }
     return line
 
@@ -516,6 +517,27 @@ def bench_flash(mla, device, peaks, batch=4, seq=4096, q_heads=64, kv_heads=8, s
     tflops = causal_pairs(seq) * batch * q_heads * 4 * 128 / seconds / 1e12
     return {"metric": "flash attention forward TFLOP/s (D=128 GQA, causal)", "value": tflops, "unit": "TFLOP/s", "ms_per_step": seconds * 1e3,
             "shape": f"B={batch} T={seq} Hq={q_heads} Hkv={kv_heads}", "frac_of_measured_sustained_peak": tflops / peaks["tensor"]}
+
+
+def bench_projection(mla, device, peaks, rows=16384, heads=128, steps=10, warmup=3):
+    """The projection GEMMs either side of the path at the prefill configuration's size (rows = 4 x 4096 tokens, H = 128):
+    latent -> per-head keys and values (tensor-bound), W_UK folded into the query and W_UV applied to the latent
+    output (both bound by HBM: their larger side is read or written once)."""
+    g = torch.Generator(device=device).manual_seed(10)
+    latent = torch.randn(rows, 512, device=device, generator=g).bfloat16()
+    w_uk = (torch.randn(heads * 128, 512, device=device, generator=g) * 0.05).bfloat16()
+    w_uv = (torch.randn(heads * 128, 512, device=device, generator=g) * 0.05).bfloat16()
+    q_nope = torch.randn(rows, heads, 128, device=device, generator=g).bfloat16()
+    o_latent = torch.randn(rows, heads, 512, device=device, generator=g).bfloat16()
+    up = time_steps(lambda: mla.up_project(latent, w_uk, w_uv, heads), steps, warmup, lambda: None) / steps
+    absorb = time_steps(lambda: mla.absorb_query(q_nope, w_uk), steps, warmup, lambda: None) / steps
+    unabsorb = time_steps(lambda: mla.unabsorb_output(o_latent, w_uv), steps, warmup, lambda: None) / steps
+    flops = 2 * rows * heads * 128 * 512
+    moved = rows * heads * (128 + 512) * 2 + heads * 128 * 512 * 2
+    return {"metric": "MLA projection GEMMs", "rows": rows, "heads": heads,
+            "up_project": {"ms": up * 1e3, "tflops": 2 * flops / up / 1e12, "bound": "tensor", "frac_of_measured_burst_peak": 2 * flops / up / 1e12 / peaks["tensor_burst"]},
+            "absorb_query": {"ms": absorb * 1e3, "gbs": moved / absorb / 1e9, "bound": "hbm", "frac": moved / absorb / 1e9 / peaks["hbm"]},
+            "unabsorb_output": {"ms": unabsorb * 1e3, "gbs": moved / unabsorb / 1e9, "bound": "hbm", "frac": moved / unabsorb / 1e9 / peaks["hbm"]}}
 
 
 def bench_rope(mla, device, peaks, batch=2, seq=8192, heads=128, steps=20, warmup=3):

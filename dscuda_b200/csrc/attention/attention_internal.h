@@ -26,6 +26,7 @@ int forward_device_status(bool reset);
 int absorbed_device_status(bool reset);
 int absorbed_backward_device_status(bool reset);
 int decode_device_status(bool reset);
+int projection_device_status(bool reset);
 int backward_device_status(bool reset);
 int append_device_status(bool reset);
 

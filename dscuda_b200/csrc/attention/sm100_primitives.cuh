@@ -162,6 +162,25 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void* tenso
         : "memory");
 }
 
+// TMA tile store shared -> global (rows / columns outside the tensor are clipped), tracked by bulk groups.
+__device__ __forceinline__ void tma_store_2d(const void* tensor_map, uint32_t smem_src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tensor_map), "r"(smem_src), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tma_store_commit() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// Returns once the stores committed so far have read their shared-memory source.
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
+// Returns once the stores committed so far are complete (written).
+__device__ __forceinline__ void tma_store_wait_all() {
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_descriptor(const void* tensor_map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
 }

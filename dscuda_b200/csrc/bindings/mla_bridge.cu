@@ -125,6 +125,20 @@ extern "C" int dscuda_mla_prefill_backward(bf16* dq, bf16* dk_nope, bf16* dk_pe,
     });
 }
 
+extern "C" int dscuda_mla_up_project(bf16* k_nope, bf16* v, const bf16* kv_latent, const bf16* w_uk, const bf16* w_uv, long long rows, int heads,
+                                     cudaStream_t stream) {
+    return guarded([&] { dscuda::mla_up_project_cuda(k_nope, v, kv_latent, w_uk, w_uv, rows, heads, stream); });
+}
+
+extern "C" int dscuda_mla_absorb_query(bf16* q_latent, const bf16* q_nope, const bf16* w_uk, long long rows, int heads, cudaStream_t stream) {
+    return guarded([&] { dscuda::mla_absorb_query_cuda(q_latent, q_nope, w_uk, rows, heads, stream); });
+}
+
+extern "C" int dscuda_mla_unabsorb_output(bf16* output, const bf16* output_latent, const bf16* w_uv, long long rows, int heads,
+                                          cudaStream_t stream) {
+    return guarded([&] { dscuda::mla_unabsorb_output_cuda(output, output_latent, w_uv, rows, heads, stream); });
+}
+
 extern "C" int dscuda_mla_device_status(int reset) {
     int status = -1;
     if (guarded([&] { status = dscuda::mla_device_status(reset != 0); }) != 0) {

@@ -30,6 +30,9 @@ MLA_SYMBOLS = {
     "dscuda_mla_prefill_forward": ([P] * 8 + [I] * 7 + [F, P], I),
     "dscuda_mla_prefill_backward_workspace_bytes": ([I] * 4, ctypes.c_size_t),
     "dscuda_mla_prefill_backward": ([P] * 14 + [I] * 7 + [F, P], I),
+    "dscuda_mla_up_project": ([P] * 5 + [ctypes.c_longlong, I, P], I),
+    "dscuda_mla_absorb_query": ([P] * 3 + [ctypes.c_longlong, I, P], I),
+    "dscuda_mla_unabsorb_output": ([P] * 3 + [ctypes.c_longlong, I, P], I),
     "dscuda_mla_device_status": ([I], I),
 }
 FLASH_SYMBOLS = {

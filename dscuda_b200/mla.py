@@ -130,6 +130,41 @@ def rope_apply(q_pe=None, k_pe=None, positions=None, theta=10000.0):
     return q_pe, k_pe
 
 
+def up_project(kv_latent, w_uk, w_uv, heads):
+    """Per-head keys and values from the latent (`dscuda_mla_up_project`): kv_latent [..., 512],
+    w_uk / w_uv [H*128, 512] -> (k_nope [..., H, 128], v [..., H, 128])."""
+    _require(kv_latent, w_uk, w_uv)
+    rows = kv_latent.numel() // kv_latent.shape[-1]
+    lead = kv_latent.shape[:-1]
+    k_nope = torch.empty(*lead, heads, 128, device=kv_latent.device, dtype=torch.bfloat16)
+    v = torch.empty_like(k_nope)
+    lib = library("mla")
+    checked(lib, "mla", lib.dscuda_mla_up_project(_ptr(k_nope), _ptr(v), _ptr(kv_latent), _ptr(w_uk), _ptr(w_uv), rows, heads, _stream()))
+    return k_nope, v
+
+
+def absorb_query(q_nope, w_uk):
+    """W_UK folded into the query (`dscuda_mla_absorb_query`): q_nope [..., H, 128], w_uk [H*128, 512] -> q_latent [..., H, 512]."""
+    _require(q_nope, w_uk)
+    heads = q_nope.shape[-2]
+    rows = q_nope.numel() // (heads * q_nope.shape[-1])
+    q_latent = torch.empty(*q_nope.shape[:-1], 512, device=q_nope.device, dtype=torch.bfloat16)
+    lib = library("mla")
+    checked(lib, "mla", lib.dscuda_mla_absorb_query(_ptr(q_latent), _ptr(q_nope), _ptr(w_uk), rows, heads, _stream()))
+    return q_latent
+
+
+def unabsorb_output(output_latent, w_uv):
+    """W_UV applied to the latent output (`dscuda_mla_unabsorb_output`): o_latent [..., H, 512], w_uv [H*128, 512] -> out [..., H, 128]."""
+    _require(output_latent, w_uv)
+    heads = output_latent.shape[-2]
+    rows = output_latent.numel() // (heads * output_latent.shape[-1])
+    out = torch.empty(*output_latent.shape[:-1], 128, device=output_latent.device, dtype=torch.bfloat16)
+    lib = library("mla")
+    checked(lib, "mla", lib.dscuda_mla_unabsorb_output(_ptr(out), _ptr(output_latent), _ptr(w_uv), rows, heads, _stream()))
+    return out
+
+
 def _prefill_dims(q_nope, cu_seqlens, max_seqlen):
     if cu_seqlens is None:
         b, s, h, _ = q_nope.shape

@@ -116,6 +116,20 @@ int dscuda_mla_prefill_backward(
     int batch, int max_sequence, int total_tokens, int heads,
     int nope, int rope, int value, float scale, void* stream);
 
+/* No counterpart in the reference (include/mla.h, mla_up_project_cuda): k_nope [rows,H,128] =
+ * kv_latent [rows,512] W_UK^T and v = kv_latent W_UV^T, weights [H*128,512]; k_nope or v may be NULL. */
+int dscuda_mla_up_project(
+    void* k_nope, void* v, const void* kv_latent, const void* w_uk, const void* w_uv,
+    long long rows, int heads, void* stream);
+
+/* No counterpart in the reference (mla_absorb_query_cuda): q_latent [rows,H,512] = q_nope [rows,H,128] W_UK[h]. */
+int dscuda_mla_absorb_query(
+    void* q_latent, const void* q_nope, const void* w_uk, long long rows, int heads, void* stream);
+
+/* No counterpart in the reference (mla_unabsorb_output_cuda): out [rows,H,128] = o_latent [rows,H,512] W_UV[h]^T. */
+int dscuda_mla_unabsorb_output(
+    void* output, const void* output_latent, const void* w_uv, long long rows, int heads, void* stream);
+
 /* No counterpart in the reference: sticky device status of the MLA kernels
  * (0 fine, 1 a bounded in-kernel wait ran out, 2 misaligned shared memory, 3 a
  * cache append skipped, or a checked decode replaced, an index outside the cache).  Synchronises the device. */

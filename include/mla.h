@@ -279,6 +279,46 @@ void mla_rope_apply_cuda(
     float theta,
     cudaStream_t stream = nullptr);
 
+// ---------------------------------------------------------------------------
+// The dense projections either side of the attention kernels (no counterpart in
+// the reference, whose benchmarks draw already-projected tensors).  W_UK and W_UV
+// are the per-head up-projection weights stored [H*128, 512] (head h is rows
+// [128h, 128h+128)); every tensor is bf16, row-major, contiguous; fp32 accumulate.
+//
+// mla_up_project_cuda: k_nope [rows, H, 128] = kv_latent [rows, 512] W_UK^T and
+//   v [rows, H, 128] = kv_latent W_UV^T (either output may be null), the inputs
+//   of mla_prefill_forward_cuda.
+// mla_absorb_query_cuda: q_latent [rows, H, 512] = q_nope [rows, H, 128] W_UK[h],
+//   the latent half of the query mla_decode_forward_cuda takes.
+// mla_unabsorb_output_cuda: out [rows, H, 128] = o_latent [rows, H, 512] W_UV[h]^T,
+//   applied to the decode output.
+// ---------------------------------------------------------------------------
+void mla_up_project_cuda(
+    __nv_bfloat16* k_nope,
+    __nv_bfloat16* v,
+    const __nv_bfloat16* kv_latent,
+    const __nv_bfloat16* w_uk,
+    const __nv_bfloat16* w_uv,
+    long long rows,
+    int heads,
+    cudaStream_t stream = nullptr);
+
+void mla_absorb_query_cuda(
+    __nv_bfloat16* q_latent,
+    const __nv_bfloat16* q_nope,
+    const __nv_bfloat16* w_uk,
+    long long rows,
+    int heads,
+    cudaStream_t stream = nullptr);
+
+void mla_unabsorb_output_cuda(
+    __nv_bfloat16* output,
+    const __nv_bfloat16* output_latent,
+    const __nv_bfloat16* w_uv,
+    long long rows,
+    int heads,
+    cudaStream_t stream = nullptr);
+
 // Sticky device status shared by the kernels above: 0 = fine, 1 = a bounded
 // pipeline wait inside a kernel ran out (results of that launch are invalid),
 // 2 = a kernel found its shared memory misaligned, 3 = a cache append skipped (or
