@@ -95,6 +95,20 @@ extern "C" int dscuda_mla_cache_append(bf16* paged_cache, const bf16* latent, co
     });
 }
 
+extern "C" int dscuda_mla_cache_append_fp8(void* paged_fp8_cache, const bf16* latent, const bf16* key_rope, const int* block_table,
+                                           const int* start_positions, const int* token_counts, int batch, int tokens, int rank, int rope,
+                                           int page_size, int pages, int cache_blocks, cudaStream_t stream) {
+    return guarded([&] {
+        dscuda::mla_cache_append_fp8_cuda(paged_fp8_cache, latent, key_rope, block_table, start_positions, token_counts, batch, tokens, rank, rope,
+                                          page_size, pages, cache_blocks, stream);
+    });
+}
+
+extern "C" int dscuda_mla_cache_dequantize_fp8(bf16* paged_cache, const void* paged_fp8_cache, long long first_row, long long rows,
+                                               cudaStream_t stream) {
+    return guarded([&] { dscuda::mla_cache_dequantize_fp8_cuda(paged_cache, paged_fp8_cache, first_row, rows, stream); });
+}
+
 extern "C" int dscuda_mla_rope_apply(bf16* q_pe, bf16* k_pe, const int* positions, long long rows, int heads, int sequence_length, int rope,
                                      float theta, cudaStream_t stream) {
     return guarded([&] { dscuda::mla_rope_apply_cuda(q_pe, k_pe, positions, rows, heads, sequence_length, rope, theta, stream); });

@@ -26,6 +26,8 @@ MLA_SYMBOLS = {
     "dscuda_mla_decode_static_capacity": ([], ctypes.c_size_t),
     "dscuda_mla_decode_static": ([P] * 6 + [I] * 7 + [F, P], I),
     "dscuda_mla_cache_append": ([P] * 6 + [I] * 7 + [P], I),
+    "dscuda_mla_cache_append_fp8": ([P] * 6 + [I] * 7 + [P], I),
+    "dscuda_mla_cache_dequantize_fp8": ([P] * 2 + [ctypes.c_longlong] * 2 + [P], I),
     "dscuda_mla_rope_apply": ([P] * 3 + [ctypes.c_longlong] + [I] * 3 + [F, P], I),
     "dscuda_mla_prefill_forward": ([P] * 8 + [I] * 7 + [F, P], I),
     "dscuda_mla_prefill_backward_workspace_bytes": ([I] * 4, ctypes.c_size_t),

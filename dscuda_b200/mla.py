@@ -112,6 +112,36 @@ def cache_append(paged_cache, kv_latent, key_rope, block_table, start_positions=
     return paged_cache
 
 
+FP8_CACHE_ROW_BYTES = 656       # 512 e4m3 + four fp32 group scales + 64 bf16 rotary values
+
+
+def cache_append_fp8(paged_fp8_cache, kv_latent, key_rope, block_table, start_positions=None, token_counts=None):
+    """`cache_append` into the FP8 cache (`dscuda_mla_cache_append_fp8`): paged_fp8_cache [blocks, page, 656] uint8."""
+    _require(paged_fp8_cache, kv_latent, key_rope, block_table, start_positions, token_counts)
+    if paged_fp8_cache.dtype != torch.uint8 or paged_fp8_cache.shape[-1] != FP8_CACHE_ROW_BYTES:
+        raise ValueError("the FP8 cache is a uint8 tensor [blocks, page, 656]")
+    b, t, rank = kv_latent.shape
+    lib = library("mla")
+    checked(lib, "mla", lib.dscuda_mla_cache_append_fp8(
+        _ptr(paged_fp8_cache), _ptr(kv_latent), _ptr(key_rope), _ptr(block_table), _ptr(start_positions), _ptr(token_counts),
+        b, t, rank, key_rope.shape[-1], paged_fp8_cache.shape[1], block_table.shape[1], paged_fp8_cache.shape[0], _stream()))
+    return paged_fp8_cache
+
+
+def cache_dequantize_fp8(paged_fp8_cache, paged_cache=None, first_row=0, rows=None):
+    """FP8 cache rows -> the bf16 cache layout the decode reads (`dscuda_mla_cache_dequantize_fp8`).
+    Rows are physical (page * page_size + slot); by default the whole cache."""
+    _require(paged_fp8_cache, paged_cache)
+    blocks, page, _ = paged_fp8_cache.shape
+    if paged_cache is None:
+        paged_cache = torch.empty(blocks, page, 1, 576, device=paged_fp8_cache.device, dtype=torch.bfloat16)
+    if rows is None:
+        rows = blocks * page - first_row
+    lib = library("mla")
+    checked(lib, "mla", lib.dscuda_mla_cache_dequantize_fp8(_ptr(paged_cache), _ptr(paged_fp8_cache), first_row, rows, _stream()))
+    return paged_cache
+
+
 def rope_apply(q_pe=None, k_pe=None, positions=None, theta=10000.0):
     """Rotary embedding in place (`dscuda_mla_rope_apply`) of q_pe [..., H, 64] and/or k_pe [..., 1, 64] (bf16).
     `positions` int32 [rows] on the device, or None for dense [B, S, ...] tensors (position = index along S)."""

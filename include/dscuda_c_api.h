@@ -88,6 +88,19 @@ int dscuda_mla_cache_append(
     int batch, int tokens, int rank, int rope, int page_size, int pages, int cache_blocks,
     void* stream);
 
+/* No counterpart in the reference (include/mla.h, mla_cache_append_fp8_cuda): dscuda_mla_cache_append
+ * into the FP8 cache format (656 bytes per token: 512 e4m3, four fp32 group scales, 64 bf16 rotary). */
+int dscuda_mla_cache_append_fp8(
+    void* paged_fp8_cache, const void* latent, const void* key_rope,
+    const int* block_table, const int* start_positions, const int* token_counts,
+    int batch, int tokens, int rank, int rope, int page_size, int pages, int cache_blocks,
+    void* stream);
+
+/* No counterpart in the reference (mla_cache_dequantize_fp8_cuda): physical rows
+ * [first_row, first_row + rows) of the FP8 cache rewritten in the bf16 layout dscuda_mla_decode reads. */
+int dscuda_mla_cache_dequantize_fp8(
+    void* paged_cache, const void* paged_fp8_cache, long long first_row, long long rows, void* stream);
+
 /* No counterpart in the reference (include/mla.h, mla_rope_apply_cuda): rotary
  * embedding in place of q_pe [rows,heads,64] and k_pe [rows,1,64]; either pointer
  * may be NULL; positions may be NULL (position = row % sequence_length). */

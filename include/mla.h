@@ -23,6 +23,9 @@ constexpr int MLA_KV_RANK = 512;
 constexpr int MLA_ROPE_SIZE = 64;
 constexpr int MLA_NOPE_SIZE = 128;
 constexpr int MLA_VALUE_SIZE = 128;
+// Bytes of one token row in the FP8 cache: 512 e4m3 values, four fp32 scales (one per 128
+// columns), 64 bf16 rotary values.
+constexpr int MLA_FP8_CACHE_ROW_BYTES = 512 + 16 + 128;
 
 // Absorbed-query causal forward.  query_latent [B,T,H,C], query_rope [B,T,H,R],
 // kv_latent [B,T,C] and key_rope [B,T,R] shared by all heads, output [B,T,H,C],
@@ -260,6 +263,38 @@ void mla_cache_append_cuda(
     int page_size,
     int pages_per_sequence,
     int cache_blocks,
+    cudaStream_t stream = nullptr);
+
+// No counterpart in the reference (unquantised; reference/python/sources.json:2).  The cache in FP8:
+// paged_fp8_cache is [cache_blocks, page_size, MLA_FP8_CACHE_ROW_BYTES] bytes, the row of a token being
+// its 512 latent values as e4m3 (value = e4m3 * scale of its 128-column group), the four fp32 scales
+// (max|x| of the group / 448, or 1 for a zero group) and its 64 rotary values in bf16.
+// mla_cache_append_fp8_cuda quantises and writes the rows of new tokens, with the arguments, addressing
+// and error behaviour of mla_cache_append_cuda.  mla_cache_dequantize_fp8_cuda rewrites the
+// physical rows [first_row, first_row + rows) (row = page * page_size + slot) into a bf16 cache
+// of the layout mla_decode_forward_cuda reads; decode over an FP8 cache is that pass followed by
+// the bf16 decode.
+void mla_cache_append_fp8_cuda(
+    void* paged_fp8_cache,
+    const __nv_bfloat16* kv_latent,
+    const __nv_bfloat16* key_rope,
+    const int* block_table,
+    const int* start_positions,
+    const int* token_counts,
+    int batch_size,
+    int tokens,
+    int kv_rank,
+    int rope_size,
+    int page_size,
+    int pages_per_sequence,
+    int cache_blocks,
+    cudaStream_t stream = nullptr);
+
+void mla_cache_dequantize_fp8_cuda(
+    __nv_bfloat16* paged_kv_cache,
+    const void* paged_fp8_cache,
+    long long first_row,
+    long long rows,
     cudaStream_t stream = nullptr);
 
 // No counterpart in the reference, whose benchmarks draw already-rotated inputs.

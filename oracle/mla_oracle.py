@@ -129,6 +129,23 @@ def paged_decode(query, paged_cache, block_table, lengths, scale, rank=512):
                             kv[..., :rank], kv[..., rank:], scale, mask)
 
 
+def quantize_fp8_rows(kv):
+    """FP8 cache rows of tokens `kv` [..., 576] bf16 (no counterpart in the reference, which is unquantised):
+    per 128-column group of the 512 latent values scale = max|x| / 448 (1 for a zero group), value / scale
+    rounded to e4m3; returns (codes uint8 [..., 512], scales fp32 [..., 4], rope bf16 [..., 64])."""
+    latent = kv[..., :512].float().reshape(*kv.shape[:-1], 4, 128)
+    amax = latent.abs().amax(dim=-1, keepdim=True)
+    scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    codes = (latent / scale).to(torch.float8_e4m3fn).view(torch.uint8).reshape(*kv.shape[:-1], 512)
+    return codes, scale.squeeze(-1).contiguous(), kv[..., 512:].contiguous()
+
+
+def dequantize_fp8_rows(codes, scales, rope):
+    """The bf16 rows [..., 576] an FP8 cache row stands for: e4m3 * scale rounded to bf16, rotary values unchanged."""
+    latent = codes.view(torch.float8_e4m3fn).float().reshape(*codes.shape[:-1], 4, 128) * scales.unsqueeze(-1)
+    return torch.cat((latent.reshape(*codes.shape[:-1], 512).bfloat16(), rope), -1)
+
+
 # --------------------------------------------------------------------------
 # Non-absorbed contract (per-head k_nope / v, shared k_pe)
 # --------------------------------------------------------------------------

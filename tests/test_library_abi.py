@@ -17,7 +17,7 @@ ROOT = pathlib.Path(__file__).resolve().parents[1]
 def declared_symbols():
     text = (ROOT / "include" / "dscuda_c_api.h").read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(dscuda_[a-z_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(dscuda_[a-z0-9_]+)\s*\(", text)))
 
 
 def test_header_declares_the_reference_bridge_symbols():
