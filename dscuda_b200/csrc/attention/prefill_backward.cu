@@ -1,23 +1,23 @@
 // Backward of the non-absorbed causal MLA attention for sm_100a.
 //
 // One call launches, on the caller's stream:
-//   1. a memset of the fp32 dk_pe accumulator (first total*64 floats of the workspace);
-//   2. delta_kernel:        delta[q] = sum_d dO[q,d] * O[q,d]            (fp32, LSE layout);
-//   3. backward_dq_kernel:  per 128-row query tile, over 128-key tiles
+//   1. delta_kernel:        delta[q] = sum_d dO[q,d] * O[q,d]            (fp32, LSE layout);
+//   2. backward_dq_kernel:  per 128-row query tile, over 128-key tiles
 //                           S = Q K^T, dP = dO V^T (tcgen05, fp32 in tensor memory, dO as a
 //                           tensor-memory operand), P = exp(S*scale - LSE),
 //                           dS = P (dP - delta) scale (registers, in two stages),
 //                           dQ += dS K with dS fed from tensor memory;
-//   4. backward_dkdv_kernel: per 128-key tile, over 64-query tiles
+//   3. backward_dkdv_kernel: per 128-key tile, over 64-query tiles
 //                           S^T = K Q^T, dP^T = V dO^T, P^T, dS^T as above (one thread per key),
-//                           dV += P^T dO, dK += dS^T Q; the rotary 64 columns of dK are
-//                           added over heads with fp32 atomics into the accumulator;
-//   5. a conversion of that accumulator to bf16 dk_pe.
+//                           dV += P^T dO, dK += dS^T Q; the rotary 64 columns of dK go, per head
+//                           and in fp32, to the workspace;
+//   4. sum_dk_pe_kernel:    those contributions added over the heads in index order -> the fp32
+//                           sums at the start of the workspace and bf16 dk_pe.
 //
 // S and dP are recomputed in both main kernels: a 128x192 dQ tile, a 128x192 dK
 // tile and a 128x128 dV tile plus the score tiles do not fit the 512 tensor
 // memory columns of one SM together, and splitting keeps every gradient a plain
-// single-writer store (only dk_pe, which sums over heads, uses atomics).
+// single-writer store: results are bit-identical from call to call.
 //
 // Both main kernels: warps 0-7 are the softmax threads (all 256 on the same tile,
 // two per row), warp 8 issues the MMAs (the whole warp runs the loop, one elected
@@ -60,7 +60,7 @@ struct BackwardParams {
     __nv_bfloat16* dq;        // [rows, H, 192]
     __nv_bfloat16* dk_nope;   // [rows, H, 128]
     __nv_bfloat16* dv;        // [rows, H, 128]
-    float* dk_pe_acc;         // [rows, 64] fp32, zeroed before the launch
+    float* dk_pe_parts;       // [rows, heads, 64] fp32: every head's dk_pe contribution, written once
     const float* lse;         // dense [B,H,S]; packed [H,total]
     const float* delta;       // same layout as lse
     const int* cu_seqlens;
@@ -194,12 +194,25 @@ __global__ void __launch_bounds__(256) delta_kernel(float* delta, const __nv_bfl
 }
 
 // ---------------------------------------------------------------------------
-// dk_pe accumulator -> bf16
+// per-head dk_pe contributions -> fp32 sums and bf16 dk_pe
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) convert_dk_pe_kernel(__nv_bfloat16* dk_pe, const float* acc, size_t elements) {
+__global__ void __launch_bounds__(256) sum_dk_pe_kernel(__nv_bfloat16* dk_pe, float* sums, const float4* parts, size_t rows, int heads) {
+    // 16 threads per key row, four columns each; the heads are added in index order, so the sum
+    // does not depend on how the CTAs of the key-side kernel were scheduled
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; index < elements; index += stride) {
-        dk_pe[index] = __float2bfloat16(acc[index]);
+    for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; index < rows * 16; index += stride) {
+        const float4* src = parts + (index / 16) * static_cast<size_t>(heads) * 16 + index % 16;
+        float4 total = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+#pragma unroll 8
+        for (int h = 0; h < heads; ++h) {
+            const float4 x = __ldg(src + static_cast<size_t>(h) * 16);
+            total.x += x.x;
+            total.y += x.y;
+            total.z += x.z;
+            total.w += x.w;
+        }
+        reinterpret_cast<float4*>(sums)[index] = total;
+        reinterpret_cast<uint2*>(dk_pe)[index] = make_uint2(pack_bf16x2(total.x, total.y), pack_bf16x2(total.z, total.w));
     }
 }
 
@@ -845,10 +858,10 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
                         if (c < 4) {
                             store_bf16_row(dk_row + c * 32, values, 32, 1.0F);
                         } else {
-                            float* acc = p.dk_pe_acc + row * 64 + (c - 4) * 32;
+                            uint4* part = reinterpret_cast<uint4*>(p.dk_pe_parts + (row * p.heads + head) * 64 + (c - 4) * 32);
 #pragma unroll
-                            for (int e = 0; e < 32; ++e) {
-                                atomicAdd(acc + e, __uint_as_float(values[e]));
+                            for (int e = 0; e < 8; ++e) {
+                                part[e] = make_uint4(values[4 * e], values[4 * e + 1], values[4 * e + 2], values[4 * e + 3]);
                             }
                         }
                     }
@@ -890,6 +903,10 @@ std::size_t accumulator_bytes(int total_tokens) {
     return (static_cast<std::size_t>(total_tokens) * 64 * sizeof(float) + 255) / 256 * 256;
 }
 
+std::size_t delta_bytes(int total_tokens, int heads) {
+    return (static_cast<std::size_t>(total_tokens) * heads * sizeof(float) + 255) / 256 * 256;
+}
+
 }  // namespace
 
 namespace internal {
@@ -913,7 +930,8 @@ std::size_t mla_prefill_backward_workspace_bytes(int batch_size, int max_sequenc
     if (total_tokens <= 0 || heads <= 0) {
         return 0;
     }
-    return accumulator_bytes(total_tokens) + static_cast<std::size_t>(total_tokens) * heads * sizeof(float);
+    // dk_pe sums, then delta [tokens, heads], then the per-head dk_pe contributions [tokens, heads, 64]
+    return accumulator_bytes(total_tokens) + delta_bytes(total_tokens, heads) + static_cast<std::size_t>(total_tokens) * heads * 64 * sizeof(float);
 }
 
 void mla_prefill_backward_cuda(__nv_bfloat16* dq, __nv_bfloat16* dk_nope, __nv_bfloat16* dk_pe, __nv_bfloat16* dv,
@@ -936,6 +954,7 @@ void mla_prefill_backward_cuda(__nv_bfloat16* dq, __nv_bfloat16* dk_nope, __nv_b
     }
     float* accumulator = static_cast<float*>(workspace);
     float* delta = reinterpret_cast<float*>(static_cast<char*>(workspace) + accumulator_bytes(total_tokens));
+    float* parts = reinterpret_cast<float*>(static_cast<char*>(workspace) + accumulator_bytes(total_tokens) + delta_bytes(total_tokens, heads));
 
     BackwardParams params{};
     const std::uint64_t rows = static_cast<std::uint64_t>(total_tokens);
@@ -956,7 +975,7 @@ void mla_prefill_backward_cuda(__nv_bfloat16* dq, __nv_bfloat16* dk_nope, __nv_b
     params.dq = dq;
     params.dk_nope = dk_nope;
     params.dv = dv;
-    params.dk_pe_acc = accumulator;
+    params.dk_pe_parts = parts;
     params.lse = logsumexp;
     params.delta = delta;
     params.cu_seqlens = cu_seqlens;
@@ -968,7 +987,6 @@ void mla_prefill_backward_cuda(__nv_bfloat16* dq, __nv_bfloat16* dk_nope, __nv_b
     params.scale_log2 = scale * LOG2E;
     configure_kernels();
 
-    CUDA_CHECK(cudaMemsetAsync(accumulator, 0, static_cast<std::size_t>(total_tokens) * 64 * sizeof(float), stream));
     const std::size_t pairs = static_cast<std::size_t>(total_tokens) * heads;
     const unsigned delta_blocks = static_cast<unsigned>(pairs / 8 + 1 < 148 * 32 ? pairs / 8 + 1 : 148 * 32);
     delta_kernel<<<delta_blocks, 256, 0, stream>>>(delta, output_gradient, output, cu_seqlens, batch_size, max_sequence_length, total_tokens, heads);
@@ -984,9 +1002,9 @@ void mla_prefill_backward_cuda(__nv_bfloat16* dq, __nv_bfloat16* dk_nope, __nv_b
     CUDA_CHECK(cudaGetLastError());
     backward_dkdv_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(params);
     CUDA_CHECK(cudaGetLastError());
-    const std::size_t elements = static_cast<std::size_t>(total_tokens) * 64;
-    const unsigned convert_blocks = static_cast<unsigned>(elements / 256 + 1 < 148 * 8 ? elements / 256 + 1 : 148 * 8);
-    convert_dk_pe_kernel<<<convert_blocks, 256, 0, stream>>>(dk_pe, accumulator, elements);
+    const std::size_t quads = static_cast<std::size_t>(total_tokens) * 16;
+    const unsigned sum_blocks = static_cast<unsigned>(quads / 256 + 1 < 148 * 8 ? quads / 256 + 1 : 148 * 8);
+    sum_dk_pe_kernel<<<sum_blocks, 256, 0, stream>>>(dk_pe, accumulator, reinterpret_cast<const float4*>(parts), static_cast<std::size_t>(total_tokens), heads);
     CUDA_CHECK(cudaGetLastError());
 }
 

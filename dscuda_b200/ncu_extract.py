@@ -42,7 +42,7 @@ KERNEL_PATTERNS = (
     (r"backward_dq_kernel", "prefill_bwd_dq"),
     (r"backward_dkdv_kernel", "prefill_bwd_dkdv"),
     (r"absorbed_delta_kernel", "absorbed_delta"),
-    (r"convert_dk_pe_kernel", "dk_pe_convert"),
+    (r"sum_dk_pe_kernel", "dk_pe_sum"),
     (r"(?<!absorbed_)delta_kernel", "prefill_delta"),
     (r"absorbed_attention_kernel", "absorbed_fwd_decode"),
     (r"decode_combine_kernel", "decode_combine"),

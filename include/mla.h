@@ -211,7 +211,9 @@ std::size_t mla_prefill_backward_workspace_bytes(
 // pe), dk_nope [..,H,128], dk_pe [..,1,64] (summed over the heads of this call)
 // and dv [..,H,128], all BF16.  The first total_tokens*64 FP32 values of the
 // workspace hold the unrounded dk_pe sums afterwards, for callers that shard
-// heads over several GPUs and add the partial sums themselves.
+// heads over several GPUs and add the partial sums themselves.  No output is
+// accumulated with atomics (dk_pe adds the heads in index order), so two calls
+// on the same inputs return the same bits.
 void mla_prefill_backward_cuda(
     __nv_bfloat16* dq,
     __nv_bfloat16* dk_nope,
