@@ -44,6 +44,7 @@ constexpr int STAGES = 3;
 constexpr int STAGE_BYTES = 5 * SUB_CHUNK;   // 3 chunks of QK width + 2 chunks of V width
 constexpr int RESIDENT_BYTES = 5 * BIG_CHUNK;
 constexpr int MISC_BYTES = 2048;
+constexpr int DS_TILE_BYTES = BIG * SUB * 2;  // one [128 keys x 64 queries] bf16 tile of dS^T in the scratch
 constexpr int SMEM_BYTES = RESIDENT_BYTES + STAGES * STAGE_BYTES + MISC_BYTES + 1024;
 constexpr int THREADS = 320;
 constexpr int MMA_WARP = 8;
@@ -63,6 +64,16 @@ struct BackwardParams {
     float* dk_pe_parts;       // [rows, heads, 64] fp32: every head's dk_pe contribution, written once
     const float* lse;         // dense [B,H,S]; packed [H,total]
     const float* delta;       // same layout as lse
+    // Dense batches only: dS^T of the heads [head0, head0 + gridDim.y) goes to this scratch and dQ is
+    // computed from it by backward_dq_stream_kernel.  Null: backward_dq_kernel recomputes S and dP.
+    // The scratch is a sequence of 16 KB tiles, one per (128-key tile kt, 64-query tile qt >= 2 kt):
+    // tile number kt * QT - kt * (kt - 1) + (qt - 2 kt) of its (batch, head), QT = ds_pitch / 64.  Inside a
+    // tile: [8 blocks of 8 queries][128 keys][8 bf16], the layout tcgen05 reads without a swizzle as an
+    // MN-major operand (8 keys x 16 bytes form a core matrix).
+    CUtensorMap ds_map;       // the scratch as rows of 256 64-bit words (one 8-query block of a tile), boxes of 16 rows x 128 words
+    __nv_bfloat16* ds_scratch;
+    int ds_pitch;             // the sequence length rounded up to 128
+    int head0;
     const int* cu_seqlens;
     int batch;
     int max_seq;
@@ -581,7 +592,7 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
     if (*reinterpret_cast<volatile int*>(&backward_status) != 0) {
         return;
     }
-    const int head = blockIdx.y;
+    const int head = p.head0 + blockIdx.y;
     int row0, length, block, blocks_in_sequence;
     size_t lse_offset;
     if (!locate_block(p, BIG, blockIdx.x, row0, length, block, blocks_in_sequence, lse_offset, head)) {
@@ -761,6 +772,13 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
         const int r = threadIdx.x % BIG;
         const uint32_t lane_base = static_cast<uint32_t>((warp % 4) * 32) << 16;
         const int key_pos = key_start + r;
+        uint4* ds_tiles = nullptr;             // this key tile's first tile of the scratch (query tile 2 * block)
+        if (p.ds_scratch != nullptr) {
+            const size_t key_tiles = p.ds_pitch / BIG;
+            const size_t first = (static_cast<size_t>(blockIdx.z) * gridDim.y + blockIdx.y) * (key_tiles * key_tiles + key_tiles) +
+                                 static_cast<size_t>(block) * (2 * key_tiles) - static_cast<size_t>(block) * static_cast<size_t>(block > 0 ? block - 1 : 0);
+            ds_tiles = reinterpret_cast<uint4*>(p.ds_scratch) + first * (DS_TILE_BYTES / 16);
+        }
         bool alive = true;
         // Both groups work on every tile: thread = (key row, 32 of the tile's 64 queries), so a
         // tile's softmax takes half as long and the tensor core rarely waits for it.  Each
@@ -828,6 +846,17 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&bars->soft_b[t & 1]));
+            if (ds_tiles != nullptr) {
+                // The same 32 bf16 values go to the scratch for the kernel that turns dS into dQ: four 16-byte
+                // units, unit (4 group + e) of this key.  The 32 lanes of a warp write 512 consecutive bytes.
+                // Keys past the end of the sequence are written as zeros, so that whatever lies behind
+                // the last key in the K tensor cannot reach dQ.
+                uint4* dst = ds_tiles + static_cast<size_t>(t) * (DS_TILE_BYTES / 16) + (group * 4) * BIG + r;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    dst[e * BIG] = key_pos < length ? make_uint4(packed[4 * e], packed[4 * e + 1], packed[4 * e + 2], packed[4 * e + 3]) : make_uint4(0, 0, 0, 0);
+                }
+            }
         }
         if (alive) {
             alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->final_full), 0, abort_flag, &backward_status));
@@ -884,6 +913,186 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
     }
 }
 
+// ---------------------------------------------------------------------------
+// dQ from stored dS (dense batches): dQ[q, :] = sum over keys <= q of dS[q, key] * K[key, :].
+//
+// backward_dkdv_kernel has written dS^T (scale included, zeros above the diagonal) to the
+// scratch, so this is a causal batched GEMM with nothing to recompute: 384 FLOP per (query,
+// key) pair instead of the 1024 of backward_dq_kernel.  CTA = 256 query rows of one (batch,
+// head), two 128 x 192 fp32 accumulators in tensor memory; it streams 64-key stages, each the
+// 64 keys x 256 queries of dS^T (32 blocks of 8 queries, 1 KB each: an unswizzled MN-major A
+// operand) and the [64 keys x 192] rows of K (three swizzled chunks, the MN-major B operand).
+// 56 KB per stage, four stages.  Warps 0-3 store the result, warp 4 issues the MMAs, warp 5
+// loads.  The kernel is bound by reading dS once from HBM.
+// ---------------------------------------------------------------------------
+namespace dqs {
+constexpr int QROWS = 256;
+constexpr int KSUB = 64;
+constexpr int DS_BYTES = 4 * SUB_CHUNK;
+constexpr int K_BYTES = 3 * SUB_CHUNK;
+constexpr int DQS_STAGE_BYTES = DS_BYTES + K_BYTES;
+constexpr int DQS_STAGES = 4;
+constexpr int DQS_BAR_BYTES = 1024;
+constexpr int DQS_SMEM_BYTES = DQS_STAGES * DQS_STAGE_BYTES + DQS_BAR_BYTES + 1024;
+constexpr int DQS_THREADS = 192;
+constexpr int DQS_MMA_WARP = 4;
+constexpr int DQS_LOAD_WARP = 5;
+static_assert(DQS_SMEM_BYTES <= 227 * 1024, "streamed dQ kernel shared memory");
+
+struct StreamBarriers {
+    uint64_t full[DQS_STAGES];
+    uint64_t empty[DQS_STAGES];
+    uint64_t done;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+static_assert(sizeof(StreamBarriers) <= DQS_BAR_BYTES, "barrier block too large");
+}  // namespace dqs
+
+__global__ void __launch_bounds__(dqs::DQS_THREADS, 1) backward_dq_stream_kernel(const __grid_constant__ BackwardParams p) {
+        using namespace dqs;
+    extern __shared__ uint8_t smem_raw[];
+    if (*reinterpret_cast<volatile int*>(&backward_status) != 0) {
+        return;
+    }
+    const int head = p.head0 + blockIdx.y;
+    const int length = p.max_seq;
+    const int row0 = blockIdx.z * p.max_seq;
+    const int q_tiles = (length + QROWS - 1) / QROWS;
+    const int q_start = (q_tiles - 1 - static_cast<int>(blockIdx.x)) * QROWS;        // longest first
+    const int key_end = min(length, q_start + QROWS);
+    const int stage_count = (key_end + KSUB - 1) / KSUB;
+    const bool second_used = q_start + 128 < length;
+    // rows of the scratch view (8-query blocks) before this (batch, head), and query tiles per key tile
+    const int key_tiles = p.ds_pitch / BIG;
+    const long long ds_row0 = static_cast<long long>(blockIdx.z * gridDim.y + blockIdx.y) * (key_tiles * key_tiles + key_tiles) * 8;
+    const int q_tile0 = q_start / SUB;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023U) & ~1023U;
+    uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    StreamBarriers* bars = reinterpret_cast<StreamBarriers*>(smem_aligned + DQS_STAGES * DQS_STAGE_BYTES);
+    volatile int* abort_flag = &bars->abort_flag;
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < DQS_STAGES; ++i) {
+            mbar_init(smem_u32(&bars->full[i]), 1);
+            mbar_init(smem_u32(&bars->empty[i]), 1);
+        }
+        mbar_init(smem_u32(&bars->done), 1);
+        bars->abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == DQS_MMA_WARP) {
+        tmem_alloc(smem_u32(&bars->tmem_base), TMEM_COLUMNS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+    // A stage holds keys [64 s, 64 s + 64).  The first accumulator (rows q_start..q_start+127)
+    // takes keys below q_start + 128, the second all of them; stages only the second uses
+    // load the two chunks of its rows only.
+    if (warp == DQS_LOAD_WARP) {
+        const uint64_t policy = l2_evict_first_policy();       // dS is read once; the K rows are what should stay in L2
+        bool alive = true;
+        for (int s = 0; s < stage_count && alive; ++s) {
+            const int stage = s % DQS_STAGES;
+            if (s >= DQS_STAGES) {
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->empty[stage]), ((s / DQS_STAGES) - 1) & 1, abort_flag, &backward_status));
+                if (!alive) {
+                    break;
+                }
+            }
+            if (lane == 0) {
+                const int key0 = s * KSUB;
+                const int first_chunk = key0 < q_start + 128 ? 0 : 2;
+                const uint32_t full = smem_u32(&bars->full[stage]);
+                const uint32_t dst = smem_base + stage * DQS_STAGE_BYTES;
+                mbar_arrive_expect_tx(full, (4 - first_chunk) * SUB_CHUNK + K_BYTES);
+                // key tile kt holds its query tiles 2 kt, 2 kt + 1, ... one after the other, 8 rows of the view each
+                const int kt = key0 / BIG;
+                const long long tile = static_cast<long long>(kt) * (2 * key_tiles) - static_cast<long long>(kt) * (kt - 1) + (q_tile0 - 2 * kt);
+                for (int c = first_chunk; c < 4; c += 2) {
+                    tma_load_2d_hint(dst + c * SUB_CHUNK, &p.ds_map, full, (key0 % BIG) * 2, static_cast<int>(ds_row0 + (tile + c) * 8), policy);
+                }
+                const int y = row0 + key0;
+                tma_load_2d(dst + DS_BYTES, &p.k_main_sub, full, head * 128, y);
+                tma_load_2d(dst + DS_BYTES + SUB_CHUNK, &p.k_main_sub, full, head * 128 + 64, y);
+                tma_load_2d(dst + DS_BYTES + 2 * SUB_CHUNK, &p.k_pe_sub, full, 0, y);
+            }
+        }
+    } else if (warp == DQS_MMA_WARP) {
+        const uint32_t leader = elect_one();
+        constexpr uint32_t IDESC = make_idesc_bf16(128, 192, true, true);
+        bool alive = true;
+        for (int s = 0; s < stage_count && alive; ++s) {
+            const int stage = s % DQS_STAGES;
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->full[stage]), (s / DQS_STAGES) & 1, abort_flag, &backward_status));
+            if (!alive) {
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t ds_smem = smem_base + stage * DQS_STAGE_BYTES;
+            const uint32_t k_smem = ds_smem + DS_BYTES;
+            const int key0 = s * KSUB;
+            if (key0 < q_start + 128) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    mma_ss_elect(tmem_base, make_smem_desc_plain(ds_smem + k * 256, 128, 1024), make_smem_desc(k_smem + k * 2048, SUB_CHUNK, 1024), IDESC,
+                                 (s | k) != 0 ? 1U : 0U, leader);
+                }
+            }
+            if (second_used) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    mma_ss_elect(tmem_base + 192, make_smem_desc_plain(ds_smem + 2 * SUB_CHUNK + k * 256, 128, 1024),
+                                 make_smem_desc(k_smem + k * 2048, SUB_CHUNK, 1024), IDESC, (s | k) != 0 ? 1U : 0U, leader);
+                }
+            }
+            mma_commit_elect(smem_u32(&bars->empty[stage]), leader);
+        }
+        if (alive) {
+            mma_commit_elect(smem_u32(&bars->done), leader);
+        }
+    } else {
+        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        const bool alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->done), 0, abort_flag, &backward_status));
+        if (alive) {
+            tc_fence_after_sync();
+            for (int j = 0; j < (second_used ? 2 : 1); ++j) {
+                const int q_pos = q_start + j * 128 + warp * 32 + lane;
+                __nv_bfloat16* dq_row = p.dq + (static_cast<size_t>(row0 + q_pos) * p.heads + head) * 192;
+#pragma unroll
+                for (int c = 0; c < 6; ++c) {
+                    uint32_t values[32];
+                    tmem_ld_x32(tmem_base + lane_base + j * 192 + c * 32, values);
+                    tmem_wait_ld();
+                    if (q_pos < length) {
+                        store_bf16_row(dq_row + c * 32, values, 32, 1.0F);
+                    }
+                }
+            }
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag != 0) {
+        for (int k = 0; k < 64; ++k) {
+            __nanosleep(1000);
+        }
+    }
+    if (warp == DQS_MMA_WARP) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLUMNS);
+    }
+}
+
 void configure_kernels() {
     static bool done[16] = {};
     int device = 0;
@@ -893,6 +1102,7 @@ void configure_kernels() {
     }
     CUDA_CHECK(cudaFuncSetAttribute(backward_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dqk::SMEM_BYTES));
     CUDA_CHECK(cudaFuncSetAttribute(backward_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    CUDA_CHECK(cudaFuncSetAttribute(backward_dq_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dqs::DQS_SMEM_BYTES));
     if (device < 16) {
         done[device] = true;
     }
@@ -905,6 +1115,34 @@ std::size_t accumulator_bytes(int total_tokens) {
 
 std::size_t delta_bytes(int total_tokens, int heads) {
     return (static_cast<std::size_t>(total_tokens) * heads * sizeof(float) + 255) / 256 * 256;
+}
+
+std::size_t parts_bytes(int total_tokens, int heads) {
+    return (static_cast<std::size_t>(total_tokens) * heads * 64 * sizeof(float) + 255) / 256 * 256;
+}
+
+// Dense batches keep dS^T of a group of heads in scratch between the two main kernels.  The
+// group is as many heads as fit in DS_SCRATCH_LIMIT; 0 = not even one head fits (or the batch
+// is packed), and the backward recomputes S and dP in a dQ kernel of its own instead.
+constexpr std::size_t DS_SCRATCH_LIMIT = std::size_t{20} << 30;
+
+int ds_pitch(int max_sequence_length) {
+    return (max_sequence_length + 127) / 128 * 128;
+}
+
+// 16 KB tiles of dS^T per (batch, head): key tile kt keeps its query tiles 2 kt .. QT - 1
+std::size_t ds_tiles_per_head(int max_sequence_length) {
+    const std::size_t key_tiles = static_cast<std::size_t>(ds_pitch(max_sequence_length)) / BIG;
+    return key_tiles * key_tiles + key_tiles;
+}
+
+int ds_group_heads(int batch_size, int max_sequence_length, int total_tokens, int heads) {
+    if (static_cast<long long>(batch_size) * max_sequence_length != total_tokens) {
+        return 0;
+    }
+    const std::size_t per_head = static_cast<std::size_t>(batch_size) * ds_tiles_per_head(max_sequence_length) * DS_TILE_BYTES;
+    const std::size_t fit = DS_SCRATCH_LIMIT / per_head;
+    return static_cast<int>(fit < static_cast<std::size_t>(heads) ? fit : static_cast<std::size_t>(heads));
 }
 
 }  // namespace
@@ -925,13 +1163,14 @@ int backward_device_status(bool reset) {
 }  // namespace internal
 
 std::size_t mla_prefill_backward_workspace_bytes(int batch_size, int max_sequence_length, int total_tokens, int heads) {
-    (void)batch_size;
-    (void)max_sequence_length;
     if (total_tokens <= 0 || heads <= 0) {
         return 0;
     }
-    // dk_pe sums, then delta [tokens, heads], then the per-head dk_pe contributions [tokens, heads, 64]
-    return accumulator_bytes(total_tokens) + delta_bytes(total_tokens, heads) + static_cast<std::size_t>(total_tokens) * heads * 64 * sizeof(float);
+    // dk_pe sums, then delta [tokens, heads], then the per-head dk_pe contributions [tokens, heads, 64],
+    // then (dense batches) dS^T of one group of heads
+    const std::size_t scratch = static_cast<std::size_t>(ds_group_heads(batch_size, max_sequence_length, total_tokens, heads)) * batch_size *
+                                ds_tiles_per_head(max_sequence_length) * DS_TILE_BYTES;
+    return accumulator_bytes(total_tokens) + delta_bytes(total_tokens, heads) + parts_bytes(total_tokens, heads) + scratch;
 }
 
 void mla_prefill_backward_cuda(__nv_bfloat16* dq, __nv_bfloat16* dk_nope, __nv_bfloat16* dk_pe, __nv_bfloat16* dv,
@@ -992,16 +1231,38 @@ void mla_prefill_backward_cuda(__nv_bfloat16* dq, __nv_bfloat16* dk_nope, __nv_b
     delta_kernel<<<delta_blocks, 256, 0, stream>>>(delta, output_gradient, output, cu_seqlens, batch_size, max_sequence_length, total_tokens, heads);
     CUDA_CHECK(cudaGetLastError());
 
-    dim3 grid;
-    if (cu_seqlens == nullptr) {
-        grid = dim3((max_sequence_length + BIG - 1) / BIG, heads, batch_size);
+    const int group = cu_seqlens == nullptr ? ds_group_heads(batch_size, max_sequence_length, total_tokens, heads) : 0;
+    if (group > 0) {
+        // dense: per group of heads, the key-side kernel (which leaves dS^T in the scratch) and then dQ from it
+        const int pitch = ds_pitch(max_sequence_length);
+        params.ds_scratch = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(workspace) + accumulator_bytes(total_tokens) + delta_bytes(total_tokens, heads) +
+                                                             parts_bytes(total_tokens, heads));
+        params.ds_pitch = pitch;
+        params.ds_map = make_u64_rows_map(params.ds_scratch, static_cast<std::uint64_t>(batch_size) * group * ds_tiles_per_head(max_sequence_length) * 8, 256,
+                                          128, 16);
+        for (int head0 = 0; head0 < heads; head0 += group) {
+            const int count = heads - head0 < group ? heads - head0 : group;
+            params.head0 = head0;
+            backward_dkdv_kernel<<<dim3((max_sequence_length + BIG - 1) / BIG, count, batch_size), THREADS, SMEM_BYTES, stream>>>(params);
+            CUDA_CHECK(cudaGetLastError());
+            backward_dq_stream_kernel<<<dim3((max_sequence_length + dqs::QROWS - 1) / dqs::QROWS, count, batch_size), dqs::DQS_THREADS, dqs::DQS_SMEM_BYTES, stream>>>(
+                params);
+            CUDA_CHECK(cudaGetLastError());
+        }
     } else {
-        grid = dim3(total_tokens / BIG + batch_size, heads, 1);
+        dim3 grid;
+        if (cu_seqlens == nullptr) {
+            grid = dim3((max_sequence_length + BIG - 1) / BIG, heads, batch_size);
+        } else {
+            grid = dim3(total_tokens / BIG + batch_size, heads, 1);
+        }
+        params.ds_scratch = nullptr;
+        params.head0 = 0;
+        backward_dq_kernel<<<grid, THREADS, dqk::SMEM_BYTES, stream>>>(params);
+        CUDA_CHECK(cudaGetLastError());
+        backward_dkdv_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(params);
+        CUDA_CHECK(cudaGetLastError());
     }
-    backward_dq_kernel<<<grid, THREADS, dqk::SMEM_BYTES, stream>>>(params);
-    CUDA_CHECK(cudaGetLastError());
-    backward_dkdv_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(params);
-    CUDA_CHECK(cudaGetLastError());
     const std::size_t quads = static_cast<std::size_t>(total_tokens) * 16;
     const unsigned sum_blocks = static_cast<unsigned>(quads / 256 + 1 < 148 * 8 ? quads / 256 + 1 : 148 * 8);
     sum_dk_pe_kernel<<<sum_blocks, 256, 0, stream>>>(dk_pe, accumulator, reinterpret_cast<const float4*>(parts), static_cast<std::size_t>(total_tokens), heads);

@@ -154,6 +154,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* tenso
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t smem_dst, const void* tensor_map, uint32_t bar, int x, int y, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(smem_dst), "l"(tensor_map), "r"(bar), "r"(x), "r"(y), "l"(policy)
+        : "memory");
+}
+
 // 3-D form: coordinates {x (element), y (row), z (chunk)}.
 __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void* tensor_map, uint32_t bar, int x, int y, int z) {
     asm volatile(
@@ -165,6 +172,19 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void* tenso
 // TMA tile store shared -> global (rows / columns outside the tensor are clipped), tracked by bulk groups.
 __device__ __forceinline__ void tma_store_2d(const void* tensor_map, uint32_t smem_src, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tensor_map), "r"(smem_src), "r"(x), "r"(y) : "memory");
+}
+
+// A cache policy for data that is written or read once: first in line for eviction from L2.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+
+__device__ __forceinline__ void tma_store_2d_hint(const void* tensor_map, uint32_t smem_src, int x, int y, uint64_t policy) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(tensor_map), "r"(smem_src), "r"(x),
+                 "r"(y), "l"(policy)
+                 : "memory");
 }
 
 __device__ __forceinline__ void tma_store_commit() {
@@ -339,6 +359,16 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
            (static_cast<uint64_t>((leading_bytes >> 4) & 0x3FFFU) << 16) |
            (static_cast<uint64_t>((stride_bytes >> 4) & 0x3FFFU) << 32) |
            (1ULL << 46) | (2ULL << 61);
+}
+
+// The same without a swizzle, for an MN-major operand stored as core matrices of 8 K indices x 16 bytes
+// (8 consecutive MN elements), 128 contiguous bytes each: the leading offset is the distance between core
+// matrices along K, the stride offset the distance between core matrices along MN.
+__device__ __forceinline__ uint64_t make_smem_desc_plain(uint32_t smem_addr, uint32_t leading_bytes, uint32_t stride_bytes) {
+    return static_cast<uint64_t>((smem_addr & 0x3FFFFU) >> 4) |
+           (static_cast<uint64_t>((leading_bytes >> 4) & 0x3FFFU) << 16) |
+           (static_cast<uint64_t>((stride_bytes >> 4) & 0x3FFFU) << 32) |
+           (1ULL << 46);
 }
 
 __device__ __forceinline__ uint64_t make_kmajor_desc(uint32_t smem_addr) {

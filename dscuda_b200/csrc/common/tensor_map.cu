@@ -76,4 +76,25 @@ CUtensorMap make_bf16_chunked_map(const void* base, std::uint64_t rows, std::uin
     return map;
 }
 
+CUtensorMap make_u64_rows_map(const void* base, std::uint64_t rows, std::uint32_t row_words, std::uint32_t box_words, std::uint32_t box_rows) {
+    if ((reinterpret_cast<std::uintptr_t>(base) & 15U) != 0 || (row_words * 8) % 16 != 0 || (box_words * 8) % 16 != 0) {
+        throw std::invalid_argument("tensor base, row length and box width must be multiples of 16 bytes");
+    }
+    if (rows == 0 || row_words == 0 || box_words == 0 || box_words > 256 || box_rows == 0 || box_rows > 256) {
+        throw std::invalid_argument("empty tensor or bad box");
+    }
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {row_words, rows};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_words) * 8};
+    const cuuint32_t box[2] = {box_words, box_rows};
+    const cuuint32_t element_strides[2] = {1, 1};
+    const CUresult result = encode_entry_point()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(base), dims, strides, box, element_strides,
+                                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (result != CUDA_SUCCESS) {
+        throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(result)));
+    }
+    return map;
+}
+
 }  // namespace dscuda

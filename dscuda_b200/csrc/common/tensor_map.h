@@ -23,4 +23,8 @@ CUtensorMap make_bf16_tile_map(const void* base, std::uint64_t rows, std::uint64
 CUtensorMap make_bf16_chunked_map(const void* base, std::uint64_t rows, std::uint32_t chunks, std::uint64_t row_stride_elements,
                                   std::uint32_t box_rows, std::uint32_t box_chunks);
 
+// A plain (unswizzled) view of `rows` rows of `row_words` 64-bit words each, rows contiguous.  One load of
+// a box {box_words, box_rows} at {word, row} lands in shared memory row after row, box_words * 8 bytes each.
+CUtensorMap make_u64_rows_map(const void* base, std::uint64_t rows, std::uint32_t row_words, std::uint32_t box_words, std::uint32_t box_rows);
+
 }  // namespace dscuda
