@@ -257,7 +257,7 @@ def run_ours(args, rank, world, device):
         workspace = mla.prefill_backward_workspace(w["batch"], w["seq"], w["batch"] * w["seq"], w["heads"], device)
         grads = (torch.empty(w["batch"], w["seq"], w["heads"], 192, device=device, dtype=torch.bfloat16),
                  torch.empty_like(x["k_nope"]), torch.empty_like(x["k_pe"]), torch.empty_like(x["v"]))
-        launches += mla.PREFILL_BACKWARD_LAUNCHES
+        launches += mla.prefill_backward_launches(w["batch"], w["seq"], w["batch"] * w["seq"], w["heads"])
 
     def forward():
         mla.prefill_forward(*fwd_in, SCALE, output=out, lse=lse)

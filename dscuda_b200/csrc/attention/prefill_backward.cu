@@ -28,6 +28,7 @@
 #include "sm100_primitives.cuh"
 #include "../common/tensor_map.h"
 
+#include <atomic>
 #include <cstddef>
 #include <stdexcept>
 
@@ -930,26 +931,26 @@ constexpr int QROWS = 256;
 constexpr int KSUB = 64;
 constexpr int DS_BYTES = 4 * SUB_CHUNK;
 constexpr int K_BYTES = 3 * SUB_CHUNK;
-constexpr int DQS_STAGE_BYTES = DS_BYTES + K_BYTES;
-constexpr int DQS_STAGES = 4;
-constexpr int DQS_BAR_BYTES = 1024;
-constexpr int DQS_SMEM_BYTES = DQS_STAGES * DQS_STAGE_BYTES + DQS_BAR_BYTES + 1024;
-constexpr int DQS_THREADS = 192;
-constexpr int DQS_MMA_WARP = 4;
-constexpr int DQS_LOAD_WARP = 5;
-static_assert(DQS_SMEM_BYTES <= 227 * 1024, "streamed dQ kernel shared memory");
+constexpr int STREAM_STAGE_BYTES = DS_BYTES + K_BYTES;
+constexpr int STREAM_STAGES = 4;
+constexpr int STREAM_BAR_BYTES = 1024;
+constexpr int STREAM_SMEM_BYTES = STREAM_STAGES * STREAM_STAGE_BYTES + STREAM_BAR_BYTES + 1024;
+constexpr int STREAM_THREADS = 192;
+constexpr int STREAM_MMA_WARP = 4;
+constexpr int STREAM_LOAD_WARP = 5;
+static_assert(STREAM_SMEM_BYTES <= 227 * 1024, "streamed dQ kernel shared memory");
 
 struct StreamBarriers {
-    uint64_t full[DQS_STAGES];
-    uint64_t empty[DQS_STAGES];
+    uint64_t full[STREAM_STAGES];
+    uint64_t empty[STREAM_STAGES];
     uint64_t done;
     uint32_t tmem_base;
     int abort_flag;
 };
-static_assert(sizeof(StreamBarriers) <= DQS_BAR_BYTES, "barrier block too large");
+static_assert(sizeof(StreamBarriers) <= STREAM_BAR_BYTES, "barrier block too large");
 }  // namespace dqs
 
-__global__ void __launch_bounds__(dqs::DQS_THREADS, 1) backward_dq_stream_kernel(const __grid_constant__ BackwardParams p) {
+__global__ void __launch_bounds__(dqs::STREAM_THREADS, 1) backward_dq_stream_kernel(const __grid_constant__ BackwardParams p) {
         using namespace dqs;
     extern __shared__ uint8_t smem_raw[];
     if (*reinterpret_cast<volatile int*>(&backward_status) != 0) {
@@ -970,13 +971,13 @@ __global__ void __launch_bounds__(dqs::DQS_THREADS, 1) backward_dq_stream_kernel
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023U) & ~1023U;
     uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-    StreamBarriers* bars = reinterpret_cast<StreamBarriers*>(smem_aligned + DQS_STAGES * DQS_STAGE_BYTES);
+    StreamBarriers* bars = reinterpret_cast<StreamBarriers*>(smem_aligned + STREAM_STAGES * STREAM_STAGE_BYTES);
     volatile int* abort_flag = &bars->abort_flag;
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < DQS_STAGES; ++i) {
+        for (int i = 0; i < STREAM_STAGES; ++i) {
             mbar_init(smem_u32(&bars->full[i]), 1);
             mbar_init(smem_u32(&bars->empty[i]), 1);
         }
@@ -984,7 +985,7 @@ __global__ void __launch_bounds__(dqs::DQS_THREADS, 1) backward_dq_stream_kernel
         bars->abort_flag = 0;
         mbar_init_fence();
     }
-    if (warp == DQS_MMA_WARP) {
+    if (warp == STREAM_MMA_WARP) {
         tmem_alloc(smem_u32(&bars->tmem_base), TMEM_COLUMNS);
         tmem_relinquish();
     }
@@ -996,13 +997,13 @@ __global__ void __launch_bounds__(dqs::DQS_THREADS, 1) backward_dq_stream_kernel
     // A stage holds keys [64 s, 64 s + 64).  The first accumulator (rows q_start..q_start+127)
     // takes keys below q_start + 128, the second all of them; stages only the second uses
     // load the two chunks of its rows only.
-    if (warp == DQS_LOAD_WARP) {
+    if (warp == STREAM_LOAD_WARP) {
         const uint64_t policy = l2_evict_first_policy();       // dS is read once; the K rows are what should stay in L2
         bool alive = true;
         for (int s = 0; s < stage_count && alive; ++s) {
-            const int stage = s % DQS_STAGES;
-            if (s >= DQS_STAGES) {
-                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->empty[stage]), ((s / DQS_STAGES) - 1) & 1, abort_flag, &backward_status));
+            const int stage = s % STREAM_STAGES;
+            if (s >= STREAM_STAGES) {
+                alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->empty[stage]), ((s / STREAM_STAGES) - 1) & 1, abort_flag, &backward_status));
                 if (!alive) {
                     break;
                 }
@@ -1011,7 +1012,7 @@ __global__ void __launch_bounds__(dqs::DQS_THREADS, 1) backward_dq_stream_kernel
                 const int key0 = s * KSUB;
                 const int first_chunk = key0 < q_start + 128 ? 0 : 2;
                 const uint32_t full = smem_u32(&bars->full[stage]);
-                const uint32_t dst = smem_base + stage * DQS_STAGE_BYTES;
+                const uint32_t dst = smem_base + stage * STREAM_STAGE_BYTES;
                 mbar_arrive_expect_tx(full, (4 - first_chunk) * SUB_CHUNK + K_BYTES);
                 // key tile kt holds its query tiles 2 kt, 2 kt + 1, ... one after the other, 8 rows of the view each
                 const int kt = key0 / BIG;
@@ -1025,18 +1026,18 @@ __global__ void __launch_bounds__(dqs::DQS_THREADS, 1) backward_dq_stream_kernel
                 tma_load_2d(dst + DS_BYTES + 2 * SUB_CHUNK, &p.k_pe_sub, full, 0, y);
             }
         }
-    } else if (warp == DQS_MMA_WARP) {
+    } else if (warp == STREAM_MMA_WARP) {
         const uint32_t leader = elect_one();
         constexpr uint32_t IDESC = make_idesc_bf16(128, 192, true, true);
         bool alive = true;
         for (int s = 0; s < stage_count && alive; ++s) {
-            const int stage = s % DQS_STAGES;
-            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->full[stage]), (s / DQS_STAGES) & 1, abort_flag, &backward_status));
+            const int stage = s % STREAM_STAGES;
+            alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&bars->full[stage]), (s / STREAM_STAGES) & 1, abort_flag, &backward_status));
             if (!alive) {
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t ds_smem = smem_base + stage * DQS_STAGE_BYTES;
+            const uint32_t ds_smem = smem_base + stage * STREAM_STAGE_BYTES;
             const uint32_t k_smem = ds_smem + DS_BYTES;
             const int key0 = s * KSUB;
             if (key0 < q_start + 128) {
@@ -1087,7 +1088,7 @@ __global__ void __launch_bounds__(dqs::DQS_THREADS, 1) backward_dq_stream_kernel
             __nanosleep(1000);
         }
     }
-    if (warp == DQS_MMA_WARP) {
+    if (warp == STREAM_MMA_WARP) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLUMNS);
     }
@@ -1102,7 +1103,7 @@ void configure_kernels() {
     }
     CUDA_CHECK(cudaFuncSetAttribute(backward_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dqk::SMEM_BYTES));
     CUDA_CHECK(cudaFuncSetAttribute(backward_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    CUDA_CHECK(cudaFuncSetAttribute(backward_dq_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dqs::DQS_SMEM_BYTES));
+    CUDA_CHECK(cudaFuncSetAttribute(backward_dq_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dqs::STREAM_SMEM_BYTES));
     if (device < 16) {
         done[device] = true;
     }
@@ -1122,9 +1123,9 @@ std::size_t parts_bytes(int total_tokens, int heads) {
 }
 
 // Dense batches keep dS^T of a group of heads in scratch between the two main kernels.  The
-// group is as many heads as fit in DS_SCRATCH_LIMIT; 0 = not even one head fits (or the batch
+// group is as many heads as fit in ds_scratch_limit (20 GiB unless the caller sets another); 0 = not even one head fits (or the batch
 // is packed), and the backward recomputes S and dP in a dQ kernel of its own instead.
-constexpr std::size_t DS_SCRATCH_LIMIT = std::size_t{20} << 30;
+std::atomic<std::size_t> ds_scratch_limit{std::size_t{20} << 30};
 
 int ds_pitch(int max_sequence_length) {
     return (max_sequence_length + 127) / 128 * 128;
@@ -1141,7 +1142,7 @@ int ds_group_heads(int batch_size, int max_sequence_length, int total_tokens, in
         return 0;
     }
     const std::size_t per_head = static_cast<std::size_t>(batch_size) * ds_tiles_per_head(max_sequence_length) * DS_TILE_BYTES;
-    const std::size_t fit = DS_SCRATCH_LIMIT / per_head;
+    const std::size_t fit = ds_scratch_limit.load() / per_head;
     return static_cast<int>(fit < static_cast<std::size_t>(heads) ? fit : static_cast<std::size_t>(heads));
 }
 
@@ -1161,6 +1162,16 @@ int backward_device_status(bool reset) {
 }
 
 }  // namespace internal
+
+std::size_t mla_prefill_backward_scratch_limit(long long bytes) {
+    return bytes < 0 ? ds_scratch_limit.load() : ds_scratch_limit.exchange(static_cast<std::size_t>(bytes));
+}
+
+int mla_prefill_backward_launches(int batch_size, int max_sequence_length, int total_tokens, int heads, bool packed) {
+    const int group = packed ? 0 : ds_group_heads(batch_size, max_sequence_length, total_tokens, heads);
+    // delta, the two main kernels (once per group of heads on the dense path), the dk_pe sum
+    return group > 0 ? 2 + 2 * ((heads + group - 1) / group) : 4;
+}
 
 std::size_t mla_prefill_backward_workspace_bytes(int batch_size, int max_sequence_length, int total_tokens, int heads) {
     if (total_tokens <= 0 || heads <= 0) {
@@ -1245,7 +1256,7 @@ void mla_prefill_backward_cuda(__nv_bfloat16* dq, __nv_bfloat16* dk_nope, __nv_b
             params.head0 = head0;
             backward_dkdv_kernel<<<dim3((max_sequence_length + BIG - 1) / BIG, count, batch_size), THREADS, SMEM_BYTES, stream>>>(params);
             CUDA_CHECK(cudaGetLastError());
-            backward_dq_stream_kernel<<<dim3((max_sequence_length + dqs::QROWS - 1) / dqs::QROWS, count, batch_size), dqs::DQS_THREADS, dqs::DQS_SMEM_BYTES, stream>>>(
+            backward_dq_stream_kernel<<<dim3((max_sequence_length + dqs::QROWS - 1) / dqs::QROWS, count, batch_size), dqs::STREAM_THREADS, dqs::STREAM_SMEM_BYTES, stream>>>(
                 params);
             CUDA_CHECK(cudaGetLastError());
         }

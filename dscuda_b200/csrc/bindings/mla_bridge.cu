@@ -124,6 +124,14 @@ extern "C" int dscuda_mla_prefill_forward(bf16* output, float* lse, const bf16* 
     });
 }
 
+extern "C" std::size_t dscuda_mla_prefill_backward_scratch_limit(long long bytes) {
+    return dscuda::mla_prefill_backward_scratch_limit(bytes);
+}
+
+extern "C" int dscuda_mla_prefill_backward_launches(int batch, int max_sequence, int total_tokens, int heads, int packed) {
+    return dscuda::mla_prefill_backward_launches(batch, max_sequence, total_tokens, heads, packed != 0);
+}
+
 extern "C" std::size_t dscuda_mla_prefill_backward_workspace_bytes(int batch, int max_sequence, int total_tokens, int heads) {
     return dscuda::mla_prefill_backward_workspace_bytes(batch, max_sequence, total_tokens, heads);
 }

@@ -31,6 +31,8 @@ MLA_SYMBOLS = {
     "dscuda_mla_rope_apply": ([P] * 3 + [ctypes.c_longlong] + [I] * 3 + [F, P], I),
     "dscuda_mla_prefill_forward": ([P] * 8 + [I] * 7 + [F, P], I),
     "dscuda_mla_prefill_backward_workspace_bytes": ([I] * 4, ctypes.c_size_t),
+    "dscuda_mla_prefill_backward_scratch_limit": ([ctypes.c_longlong], ctypes.c_size_t),
+    "dscuda_mla_prefill_backward_launches": ([I] * 5, I),
     "dscuda_mla_prefill_backward": ([P] * 14 + [I] * 7 + [F, P], I),
     "dscuda_mla_up_project": ([P] * 5 + [ctypes.c_longlong, I, P], I),
     "dscuda_mla_absorb_query": ([P] * 3 + [ctypes.c_longlong, I, P], I),

@@ -14,9 +14,16 @@ import torch
 from .library import checked, library  # noqa: F401 (re-exported for callers)
 
 
-# kernels of this library one dscuda_mla_prefill_backward call launches (delta pre-pass,
-# dQ kernel, dK/dV kernel, dk_pe conversion); the call also enqueues one memset of the accumulator
-PREFILL_BACKWARD_LAUNCHES = 4
+def prefill_backward_launches(batch, max_seq, total, heads, packed=False) -> int:
+    """Kernels one `dscuda_mla_prefill_backward` call launches: the delta pre-pass, the dk_pe sum, and
+    the two main kernels (dense batches: once per group of heads that fits the scratch limit)."""
+    return library("mla").dscuda_mla_prefill_backward_launches(batch, max_seq, total, heads, int(packed))
+
+
+def prefill_backward_scratch_limit(limit_bytes=-1) -> int:
+    """Sets the workspace the dense backward may spend on dS^T (`dscuda_mla_prefill_backward_scratch_limit`);
+    returns the previous limit.  0 selects the recomputing dQ kernel, a negative value only reads."""
+    return library("mla").dscuda_mla_prefill_backward_scratch_limit(limit_bytes)
 
 
 def _stream() -> int:

@@ -116,6 +116,13 @@ int dscuda_mla_prefill_forward(
     const int* cu_seqlens, int batch, int max_sequence, int total_tokens, int heads,
     int nope, int rope, int value, float scale, void* stream);
 
+/* No counterpart in the reference (mla_prefill_backward_scratch_limit): workspace the dense backward may
+ * use for dS^T; returns the previous limit, a negative value only reads it. */
+size_t dscuda_mla_prefill_backward_scratch_limit(long long bytes);
+
+/* No counterpart in the reference (mla_prefill_backward_launches): kernels per backward call. */
+int dscuda_mla_prefill_backward_launches(int batch, int max_sequence, int total_tokens, int heads, int packed);
+
 /* No counterpart in the reference (mla_prefill_backward_workspace_bytes). */
 size_t dscuda_mla_prefill_backward_workspace_bytes(
     int batch, int max_sequence, int total_tokens, int heads);

@@ -162,3 +162,30 @@ def test_long_context_packed_lengths(gpu):
         assert torch.equal(o1, out[:, h:h + 1]) and torch.equal(g1[0], grads[0][:, h:h + 1]) and torch.equal(g1[3], grads[3][:, h:h + 1])
         partial_sum += workspace[: total * 64 * 4].view(torch.float32).reshape(total, 64)
     assert rel_l2(partial_sum.cpu(), grads[2].float().reshape(total, 64).cpu()) <= 5e-3
+
+
+@pytest.mark.parametrize("limit_heads", [0, 1, 2])
+def test_dense_backward_paths_agree(gpu, limit_heads):
+    """Dense batches: dQ from the stored dS^T (all heads in one group, or group after group when the
+    scratch limit holds fewer heads) and dQ from the recomputing kernel (limit 0) give the same
+    gradients as the oracle, and the launch count follows the grouping."""
+    from dscuda_b200 import mla
+    b, s, h = 2, 333, 3
+    q_nope, q_pe, k_nope, k_pe, v, dout = oracle.prefill_inputs(11, b, s, h, dout_std=0.1)
+    tensors = (q_nope, q_pe, k_nope, k_pe, v)
+    device = [t.to(gpu) for t in tensors]
+    out, lse = mla.prefill_forward(*device, SCALE)
+    tiles = (s + 127) // 128
+    per_head = b * (tiles * tiles + tiles) * 16384
+    previous = mla.prefill_backward_scratch_limit(limit_heads * per_head)
+    try:
+        expected_launches = 4 if limit_heads == 0 else 2 + 2 * ((h + limit_heads - 1) // limit_heads)
+        assert mla.prefill_backward_launches(b, s, b * s, h) == expected_launches
+        assert mla.prefill_backward_launches(b, s, b * s, h, packed=True) == 4
+        grads = mla.prefill_backward(dout.to(gpu), out, lse, *device, SCALE)
+        torch.cuda.synchronize()
+        assert mla.device_status() == 0
+    finally:
+        mla.prefill_backward_scratch_limit(previous)
+    assert mla.prefill_backward_scratch_limit() == previous
+    check_grads(tuple(g.cpu() for g in grads), oracle.prefill_backward(dout, out.cpu(), lse.cpu(), *tensors, SCALE))
