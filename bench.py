@@ -55,20 +55,21 @@ WORKLOADS = {"train": workloads.CONFIGS["C3"], "prefill": workloads.CONFIGS["C2"
 def dram_traffic(kind: str, token_heads: int):
     """DRAM bytes (read + written) per launch of the dominant call, from the committed ncu capture
     summarised in profiles/traffic.json (written by `python -m dscuda_b200.ncu_extract counters ...
-    --traffic-json`): bytes per (token, head) of the reduced-size capture times the (token, head)
-    pairs of this run (the traffic grows in proportion to them).  None when the file has no entry."""
+    --traffic-json`): bytes per (token, head) of the reduced-size capture (same sequence length, fewer
+    heads) times the (token, head) pairs of this run; at a fixed sequence length the traffic grows in
+    proportion to them.  None when the file has no entry."""
     path = ROOT / "profiles" / "traffic.json"
     if not path.exists():
         return None, None
     entry = json.loads(path.read_text()).get("train_step")
     if not entry:
         return None, None
-    labels = ("prefill_bwd_dq", "prefill_bwd_dkdv") if kind == "backward" else ("prefill_fwd",)
+    labels = ("prefill_bwd_dq_stream", "prefill_bwd_dkdv") if kind == "backward" else ("prefill_fwd",)
     try:
         per_unit = sum(entry["kernels"][label]["dram_bytes_per_token_head"] for label in labels)
     except KeyError:
         return None, None
-    return per_unit * token_heads, "profiles/traffic.json (train_step): ncu capture at reduced size, scaled by (token, head) pairs"
+    return per_unit * token_heads, "profiles/traffic.json (train_step): ncu capture at S=8192 with 8 heads, scaled by (token, head) pairs"
 
 
 workload_flops = workloads.dense_flops
@@ -373,7 +374,7 @@ def run_ours(args, rank, world, device):
                 "fraction_of_ceiling": e2e_value / ceiling_value, "numa": numa},
         "gpu_launches": launches * args.steps,
         "verified": bool(all_checks) and all(all_checks), "verified_checks": verified,
-        "roofline": {"bound": "tensor", "kernel": "prefill backward (dQ + dK/dV kernels)" if w["backward"] else "attention_forward_kernel<3>",
+        "roofline": {"bound": "tensor", "kernel": "prefill backward (dK/dV kernel, then dQ streamed from the stored dS)" if w["backward"] else "attention_forward_kernel<3>",
                      "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": achieved / peaks["tensor"],
                      "peak_source": peaks["source"] + " sustained cuBLAS bf16", "frac_of_burst_peak": achieved / peaks["tensor_burst"],
                      "traffic": traffic, "traffic_source": traffic_source},

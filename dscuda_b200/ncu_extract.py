@@ -39,12 +39,15 @@ KERNEL_PATTERNS = (
     (r"attention_forward_kernel<\(?int\)?3>|attention_forward_kernel<3>", "prefill_fwd"),
     (r"attention_forward_kernel<\(?int\)?2>|attention_forward_kernel<2>", "flash_fwd"),
     (r"attention_forward_kernel", "prefill_fwd"),
+    (r"backward_dq_stream_kernel", "prefill_bwd_dq_stream"),
     (r"backward_dq_kernel", "prefill_bwd_dq"),
     (r"backward_dkdv_kernel", "prefill_bwd_dkdv"),
     (r"absorbed_delta_kernel", "absorbed_delta"),
     (r"sum_dk_pe_kernel", "dk_pe_sum"),
     (r"(?<!absorbed_)delta_kernel", "prefill_delta"),
-    (r"absorbed_attention_kernel", "absorbed_fwd_decode"),
+    (r"absorbed_attention_kernel", "absorbed_fwd"),
+    (r"absorbed_decode_kernel", "absorbed_decode"),
+    (r"cache_dequantize_fp8_kernel", "cache_dequantize_fp8"),
     (r"decode_combine_kernel", "decode_combine"),
     (r"absorbed_backward_query_kernel", "absorbed_bwd_query"),
     (r"absorbed_backward_key_kernel", "absorbed_bwd_key"),

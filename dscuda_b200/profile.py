@@ -55,14 +55,15 @@ def cases(suite: str) -> List[dict]:
         result.append(dict(name=f"absorbed_T{t}_H8", command=[str(BUILD / "benchmark_mla"), "1", str(t), "8", "512", "64"],
                            pattern="regex:absorbed_(attention|backward_query|backward_key|backward_reduce|delta)_kernel"))
         result.append(dict(name=f"decode_KV{t}_H16", command=[str(BUILD / "benchmark_mla_decode"), "2", str(t), "16", "512", "64", "8"],
-                           pattern="regex:(absorbed_attention|decode_combine)_kernel"))
+                           pattern="regex:(absorbed_decode|decode_combine)_kernel"))
     # B200-sized cases: inputs larger than the 126 MB L2, a few GB at most
     result.append(dict(name="absorbed_T2048_H16_B4", command=[str(BUILD / "benchmark_mla"), "4", "2048", "16", "512", "64"],
                        pattern="regex:absorbed_(attention|backward_query|backward_key|backward_reduce|delta)_kernel"))
     result.append(dict(name="decode_KV16384_H128_B16", command=[str(BUILD / "benchmark_mla_decode"), "16", "16384", "128", "512", "64", "8"],
-                       pattern="regex:(absorbed_attention|decode_combine)_kernel"))
-    result.append(dict(name="train_S4096_H32", command=[str(BUILD / "benchmark_mla_prefill"), "1", "4096", "32", "1"],
-                       pattern="regex:(attention_forward|backward_dq|backward_dkdv)_kernel", traffic_key="train_step", units=4096 * 32,
+                       pattern="regex:(absorbed_decode|decode_combine)_kernel"))
+    # the training step at the benchmark's sequence length (the dS^T scratch grows with its square), 8 heads
+    result.append(dict(name="train_S8192_H8", command=[str(BUILD / "benchmark_mla_prefill"), "1", "8192", "8", "1"],
+                       pattern="regex:(attention_forward|backward_dq_stream|backward_dq|backward_dkdv)_kernel", traffic_key="train_step", units=8192 * 8,
                        unit_name="token_head"))
     return result
 
@@ -95,6 +96,7 @@ def main(argv=None) -> int:
     ncu = shutil.which("ncu") or "/usr/local/cuda/bin/ncu"
     selected = [case for case in cases(args.suite) if not args.only or case["name"] in args.only.split(",")]
     args.out_dir.mkdir(parents=True, exist_ok=True)
+    args.profiles_dir.mkdir(parents=True, exist_ok=True)
     for case in selected:
         launches, report, list_cmd, count_cmd = commands(case, args.out_dir, ncu)
         if args.mode == "print":

@@ -18,7 +18,7 @@ def test_short_kernel_names():
     assert name("dscuda::<unnamed>::backward_dkdv_kernel(dscuda::<unnamed>::BackwardParams)") == "prefill_bwd_dkdv"
     assert name("dscuda::<unnamed>::delta_kernel(float *, ...)") == "prefill_delta"
     assert name("dscuda::<unnamed>::absorbed_delta_kernel(__nv_bfloat16 *, ...)") == "absorbed_delta"
-    assert name("dscuda::<unnamed>::absorbed_attention_kernel(dscuda::<unnamed>::AbsorbedParams)") == "absorbed_fwd_decode"
+    assert name("dscuda::<unnamed>::absorbed_attention_kernel(dscuda::<unnamed>::AbsorbedParams)") == "absorbed_fwd"
     assert name("dscuda::<unnamed>::decode_combine_kernel(__nv_bfloat16 *, float *, const float *, const int *, int, int)") == "decode_combine"
     assert name("dscuda::<unnamed>::absorbed_backward_key_kernel(dscuda::<unnamed>::AbsorbedBackwardParams)") == "absorbed_bwd_key"
     assert name("dscuda::<unnamed>::absorbed_backward_query_kernel(dscuda::<unnamed>::AbsorbedBackwardParams)") == "absorbed_bwd_query"
@@ -29,7 +29,7 @@ def test_launch_list_merges_per_label():
     launches = ncu_extract.read_launches((GOLDEN / "ncu_launches_sample.csv").read_text())
     assert launches and all(row["time_us"] > 0 for row in launches)
     labels = {row["label"] for row in launches}
-    assert {"absorbed_bwd_key", "absorbed_bwd_query", "absorbed_fwd_decode", "absorbed_delta"} <= labels
+    assert {"absorbed_bwd_key", "absorbed_bwd_query", "absorbed_fwd", "absorbed_delta"} <= labels
     merged = ncu_extract.merge_by_label(launches)
     assert sum(row["launches"] for row in merged) == len(launches)
     assert abs(sum(row["time_us"] for row in merged) - sum(row["time_us"] for row in launches)) < 1e-6
