@@ -28,7 +28,8 @@
 // Roles per CTA: warps 0-3 softmax / epilogue (thread = head x half of the keys; the two threads of a
 // head exchange their maxima and sums through shared memory), warp 4 issues every MMA in the
 // leader CTA (whole warp, one elected lane) and in the other CTA relays "loaded" events to the
-// leader, warp 5 loads with TMA.  The grid is persistent: one cluster per SM pair, the 128-key tiles
+// leader, warps 5 and 6 load with TMA (5: Q, the tiles' own keys and L2 prefetches; 6: the two small loads
+// on the critical path, rotary chunk and refill).  The grid is persistent: one cluster per SM pair, the 128-key tiles
 // of all sequences laid end to end and cut into equal ranges; a sequence cut by a range boundary
 // yields one normalised partial per range, merged by decode_combine_kernel.  Every wait is bounded.
 #include "mla.h"
@@ -62,9 +63,10 @@ constexpr int STAGES = 2;
 constexpr int STAGE_BYTES = LATENT_CHUNKS * CHUNK;
 constexpr int MISC_BYTES = 2048;
 constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + STAGES * STAGE_BYTES + CHUNK + MISC_BYTES;      // no room to realign
-constexpr int THREADS = 192;
+constexpr int THREADS = 224;
 constexpr int MMA_WARP = 4;
 constexpr int LOAD_WARP = 5;
+constexpr int REFILL_WARP = 6;
 constexpr int TMEM_COLUMNS = 512;
 constexpr uint32_t TMEM_O = 0;                  // 2 x 128 columns
 constexpr uint32_t TMEM_S = 256;                // 2 x 64 columns
@@ -128,7 +130,8 @@ struct Shared {
     // leader only: one arrival per softmax warp of either CTA (lane 0, after the warp has synchronised): P is
     // stored.  One arrival per thread would be 128 serialised transactions on the link between the two SMs.
     uint64_t p_full;
-    // 128 softmax threads of this CTA: the two threads of a head have published their maxima / sums
+    // the four softmax warps of this CTA (lane 0, after the warp has synchronised): the two threads of a head have
+    // published their maxima / sums
     uint64_t max_ready[2];
     uint64_t sum_ready;
     uint32_t tmem_base;
@@ -340,9 +343,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
         mbar_init(smem_u32(&sh->p_free), 1);
         mbar_init(smem_u32(&sh->o_final), 1);
         mbar_init(smem_u32(&sh->p_full), 8);
-        mbar_init(smem_u32(&sh->max_ready[0]), PAIR_HEADS);
-        mbar_init(smem_u32(&sh->max_ready[1]), PAIR_HEADS);
-        mbar_init(smem_u32(&sh->sum_ready), PAIR_HEADS);
+        mbar_init(smem_u32(&sh->max_ready[0]), 4);          // one arrival per softmax warp
+        mbar_init(smem_u32(&sh->max_ready[1]), 4);
+        mbar_init(smem_u32(&sh->sum_ready), 4);
         sh->abort_flag = 0;
         mbar_init_fence();
         // ---- schedule of this cluster (splits > 1) ----------------------------------
@@ -405,32 +408,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
 
     // Chunk c of a tile's own keys lives in slot c of its stage.  CTA r keeps slots {2r, 2r+1, 4+2r, 4+2r+1}
     // (its value columns); the other four are refilled with the other CTA's keys after S.
-    if (warp == LOAD_WARP) {
-        // =================== TMA producer ===================================
+    if (warp == LOAD_WARP || warp == REFILL_WARP) {
+        // =================== TMA producers ==================================
         // Three kinds of load per tile, each free to go as soon as what it overwrites has been read:
         //   A(t): the eight latent chunks of this CTA's own keys   - after P V of tile t-2 (same stage);
-        //   R(t): the rotary chunk                                  - after S of tile t-1;
-        //   B(t): refill of the four S-only slots with the other CTA's keys - after the first half of S(t).
-        // They are issued in whatever order their conditions come true (all 32 lanes walk the loop, because
-        // the block-table entries are fetched 32 at a time, one per lane; lane 0 tests and issues).
+        //   R(t): the rotary chunk                                  - after the first four score MMAs of tile t-1;
+        //   B(t): refill of the four S-only slots with the other CTA's keys - after this CTA's half of S(t).
+        // Warp LOAD_WARP issues Q, A and the L2 prefetches; warp REFILL_WARP issues R and B, which sit on the
+        // critical path (S waits for R, P V for B) and must not queue behind an A load and its prefetch.  All 32
+        // lanes of a warp walk its loop, because the block-table entries are fetched 32 at a time, one per
+        // lane; lane 0 tests and issues.  Each kind is issued in tile order by one thread, so a parity test
+        // for tile t always comes after the phase of tile t - STAGES has been seen complete.
         bool alive = true;
         while (alive && next_segment(p, schedule, walker, seg, cluster, clusters)) {
             const int tile_count = seg.tile_end - seg.tile_begin;
             const int length = sequence_length(p, seg.b);
             const int last_half_start = ((length - 1) / HALF_KEYS) * HALF_KEYS;
-            const int q_row0 = seg.b * p.heads + seg.row_tile * PAIR_HEADS + static_cast<int>(rank) * CTA_HEADS;
-            if (lane == 0) {
-                // Q may be overwritten once every score MMA of the previous segment has finished
-                if (segment_index > 0) {
-                    alive = mbar_wait(smem_u32(&sh->o_final), (segment_index - 1) & 1, abort_flag, &decode_status);
-                }
-                if (alive) {
-                    const uint32_t bar = smem_u32(&sh->q_full);
-                    mbar_arrive_expect_tx(bar, Q_BYTES);
-                    tma_load_3d(q_smem, &p.q_all, bar, 0, q_row0, 0);
-                }
-            }
-            alive = __shfl_sync(0xffffffffU, alive ? 1 : 0, 0) != 0;
             // Physical cache row (page * page_size + offset) of the first key of a 64-key half-tile of this
             // sequence.  Each kind of load walks the half-tiles in order and keeps its own window of 32 rows.
             struct Window {
@@ -450,89 +443,106 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
                 }
                 return __shfl_sync(0xffffffffU, w.rows, half_tile & 31);
             };
-            Window win_a = {0, -64}, win_r = {0, -64}, win_b = {0, -64}, win_p = {0, -64};
-            // A tile load reads 128 bytes from each of 64 cache rows (1152 bytes apart) per chunk.  The 64 rows a
-            // CTA owns in a tile are one contiguous piece of a page, so they are asked into L2 with one bulk
-            // prefetch a few tiles ahead, and the tile loads then mostly hit L2.
-            int next_p = 0;
-            auto prefetch_up_to = [&](int limit) {
-                for (; next_p < min(limit, tile_count); ++next_p) {
-                    const int row = row_of(win_p, 2 * (seg.tile_begin + next_p) + static_cast<int>(rank));
-                    if (lane == 0) {
-                        prefetch_l2_bulk(p.cache + static_cast<size_t>(row) * WIDTH, HALF_KEYS * WIDTH * 2);
-                    }
-                }
-            };
-            prefetch_up_to(PREFETCH_TILES);
-            int next_a = 0, next_r = 0, next_b = 0;         // tiles of this segment whose load of that kind is still to be issued
-            long long idle_since = clock64();
-            while (alive && (next_a < tile_count || next_r < tile_count || next_b < tile_count)) {
-                int action = 0;
+            if (warp == LOAD_WARP) {
+                const int q_row0 = seg.b * p.heads + seg.row_tile * PAIR_HEADS + static_cast<int>(rank) * CTA_HEADS;
                 if (lane == 0) {
-                    if (next_r < tile_count) {
-                        const int tile = tile_index + next_r;
-                        if (tile == 0 || mbar_test_wait(smem_u32(&sh->rope_free), (tile - 1) & 1)) {
-                            action = 2;
-                        }
+                    // Q may be overwritten once every score MMA of the previous segment has finished
+                    if (segment_index > 0) {
+                        alive = mbar_wait(smem_u32(&sh->o_final), (segment_index - 1) & 1, abort_flag, &decode_status);
                     }
-                    if (action == 0 && next_b < tile_count && next_b < next_a) {
-                        const int tile = tile_index + next_b;
-                        if (mbar_test_wait(smem_u32(&sh->refill_free[tile % STAGES]), (tile / STAGES) & 1)) {
-                            action = 3;
-                        }
-                    }
-                    if (action == 0 && next_a < tile_count) {
-                        const int tile = tile_index + next_a;
-                        if (tile < STAGES || mbar_test_wait(smem_u32(&sh->stage_free[tile % STAGES]), (tile / STAGES - 1) & 1)) {
-                            action = 1;
-                        }
-                    }
-                    if (action == 0 && (*abort_flag != 0 || clock64() - idle_since > WAIT_LIMIT_CYCLES)) {
-                        *abort_flag = 1;
-                        atomicExch(&decode_status, STATUS_WAIT_TIMEOUT);
-                        action = -1;
+                    if (alive) {
+                        const uint32_t bar = smem_u32(&sh->q_full);
+                        mbar_arrive_expect_tx(bar, Q_BYTES);
+                        tma_load_3d(q_smem, &p.q_all, bar, 0, q_row0, 0);
                     }
                 }
-                action = __shfl_sync(0xffffffffU, action, 0);
-                if (action < 0) {
-                    alive = false;
-                } else if (action == 1) {
+                alive = __shfl_sync(0xffffffffU, alive ? 1 : 0, 0) != 0;
+                Window win_a = {0, -64}, win_p = {0, -64};
+                // A tile load reads 128 bytes from each of 64 cache rows (1152 bytes apart) per chunk.  The 64 rows a
+                // CTA owns in a tile are one contiguous piece of a page, so they are asked into L2 with one bulk
+                // prefetch a few tiles ahead, and the tile loads then mostly hit L2.
+                int next_p = 0;
+                auto prefetch_up_to = [&](int limit) {
+                    for (; next_p < min(limit, tile_count); ++next_p) {
+                        const int row = row_of(win_p, 2 * (seg.tile_begin + next_p) + static_cast<int>(rank));
+                        if (lane == 0) {
+                            prefetch_l2_bulk(p.cache + static_cast<size_t>(row) * WIDTH, HALF_KEYS * WIDTH * 2);
+                        }
+                    }
+                };
+                prefetch_up_to(PREFETCH_TILES);
+                for (int next_a = 0; next_a < tile_count && alive; ++next_a) {
                     const int tile = tile_index + next_a;
                     const int stage = tile % STAGES;
                     const int row = row_of(win_a, 2 * (seg.tile_begin + next_a) + static_cast<int>(rank));
+                    if (tile >= STAGES) {
+                        alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->stage_free[stage]), (tile / STAGES - 1) & 1, abort_flag, &decode_status));
+                        if (!alive) {
+                            break;
+                        }
+                    }
                     if (lane == 0) {
                         const uint32_t bar = smem_u32(&sh->full_a[stage]);
                         mbar_arrive_expect_tx(bar, STAGE_BYTES);
                         tma_load_3d(stage_smem + stage * STAGE_BYTES, &p.k_lat8, bar, 0, row, 0);
                     }
-                    ++next_a;
-                    prefetch_up_to(next_a + PREFETCH_TILES);
-                } else if (action == 2) {
-                    const int row = row_of(win_r, 2 * (seg.tile_begin + next_r) + static_cast<int>(rank));
+                    prefetch_up_to(next_a + 1 + PREFETCH_TILES);
+                }
+            } else {
+                Window win_r = {0, -64}, win_b = {0, -64};
+                int next_r = 0, next_b = 0;         // tiles of this segment whose load of that kind is still to be issued
+                long long idle_since = clock64();
+                while (alive && (next_r < tile_count || next_b < tile_count)) {
+                    int action = 0;
                     if (lane == 0) {
-                        const uint32_t bar = smem_u32(&sh->full_r);
-                        mbar_arrive_expect_tx(bar, CHUNK);
-                        tma_load_2d(rope_smem, &p.k_rope, bar, 0, row);
-                    }
-                    ++next_r;
-                } else if (action == 3) {
-                    const int tile = tile_index + next_b;
-                    const int stage = tile % STAGES;
-                    const int row = row_of(win_b, 2 * (seg.tile_begin + next_b) + static_cast<int>(peer));
-                    if (lane == 0) {
-                        const uint32_t bar = smem_u32(&sh->full_b[stage]);
-                        mbar_arrive_expect_tx(bar, 4 * CHUNK);
-                        for (int a = 0; a < 2; ++a) {
-                            // the other CTA's keys, this CTA's value columns -> the two adjacent slots only S needed
-                            const int chunk = 4 * a + 2 * static_cast<int>(rank);
-                            const int slot = 4 * a + 2 * static_cast<int>(peer);
-                            tma_load_3d(stage_smem + stage * STAGE_BYTES + slot * CHUNK, &p.k_lat2, bar, 0, row, chunk);
+                        if (next_r < tile_count) {
+                            const int tile = tile_index + next_r;
+                            if (tile == 0 || mbar_test_wait(smem_u32(&sh->rope_free), (tile - 1) & 1)) {
+                                action = 2;
+                            }
+                        }
+                        if (action == 0 && next_b < tile_count) {
+                            const int tile = tile_index + next_b;
+                            if (mbar_test_wait(smem_u32(&sh->refill_free[tile % STAGES]), (tile / STAGES) & 1)) {
+                                action = 3;
+                            }
+                        }
+                        if (action == 0 && (*abort_flag != 0 || clock64() - idle_since > WAIT_LIMIT_CYCLES)) {
+                            *abort_flag = 1;
+                            atomicExch(&decode_status, STATUS_WAIT_TIMEOUT);
+                            action = -1;
                         }
                     }
-                    ++next_b;
-                }
-                if (action > 0) {
-                    idle_since = clock64();
+                    action = __shfl_sync(0xffffffffU, action, 0);
+                    if (action < 0) {
+                        alive = false;
+                    } else if (action == 2) {
+                        const int row = row_of(win_r, 2 * (seg.tile_begin + next_r) + static_cast<int>(rank));
+                        if (lane == 0) {
+                            const uint32_t bar = smem_u32(&sh->full_r);
+                            mbar_arrive_expect_tx(bar, CHUNK);
+                            tma_load_2d(rope_smem, &p.k_rope, bar, 0, row);
+                        }
+                        ++next_r;
+                    } else if (action == 3) {
+                        const int tile = tile_index + next_b;
+                        const int stage = tile % STAGES;
+                        const int row = row_of(win_b, 2 * (seg.tile_begin + next_b) + static_cast<int>(peer));
+                        if (lane == 0) {
+                            const uint32_t bar = smem_u32(&sh->full_b[stage]);
+                            mbar_arrive_expect_tx(bar, 4 * CHUNK);
+                            for (int a = 0; a < 2; ++a) {
+                                // the other CTA's keys, this CTA's value columns -> the two adjacent slots only S needed
+                                const int chunk = 4 * a + 2 * static_cast<int>(rank);
+                                const int slot = 4 * a + 2 * static_cast<int>(peer);
+                                tma_load_3d(stage_smem + stage * STAGE_BYTES + slot * CHUNK, &p.k_lat2, bar, 0, row, chunk);
+                            }
+                        }
+                        ++next_b;
+                    }
+                    if (action > 0) {
+                        idle_since = clock64();
+                    }
                 }
             }
             tile_index += tile_count;
@@ -767,7 +777,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
                 // arrival on the other parity's barrier in between.
                 float tile_max = fmaxf(fmaxf(mx0, mx2), fmaxf(mx1, mx3));
                 sh->maxima[tile & 1][r] = tile_max;
-                mbar_arrive(smem_u32(&sh->max_ready[tile & 1]));
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(smem_u32(&sh->max_ready[tile & 1]));
+                }
                 alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->max_ready[tile & 1]), (tile >> 1) & 1, abort_flag, &decode_status));
                 if (!alive) {
                     break;
@@ -870,7 +883,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) absorbed
             // the head's row sum is the sum of its two threads' sums (the buffer is free: every thread has
             // been through the tiles of this segment since it last read it)
             sh->sums[r] = l_sum;
-            mbar_arrive(smem_u32(&sh->sum_ready));
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&sh->sum_ready));
+            }
             alive = __all_sync(0xffffffffU, mbar_wait(smem_u32(&sh->sum_ready), segment_index & 1, abort_flag, &decode_status));
             if (!alive) {
                 break;
