@@ -65,15 +65,14 @@ struct BackwardParams {
     float* dk_pe_parts;       // [rows, heads, 64] fp32: every head's dk_pe contribution, written once
     const float* lse;         // dense [B,H,S]; packed [H,total]
     const float* delta;       // same layout as lse
-    // Dense batches only: dS^T of the heads [head0, head0 + gridDim.y) goes to this scratch and dQ is
-    // computed from it by backward_dq_stream_kernel.  Null: backward_dq_kernel recomputes S and dP.
-    // The scratch is a sequence of 16 KB tiles, one per (128-key tile kt, 64-query tile qt >= 2 kt):
-    // tile number kt * QT - kt * (kt - 1) + (qt - 2 kt) of its (batch, head), QT = ds_pitch / 64.  Inside a
-    // tile: [8 blocks of 8 queries][128 keys][8 bf16], the layout tcgen05 reads without a swizzle as an
-    // MN-major operand (8 keys x 16 bytes form a core matrix).
+    // dS^T of the heads [head0, head0 + gridDim.y) goes to this scratch and dQ is computed from it by
+    // backward_dq_stream_kernel.  Null: backward_dq_kernel recomputes S and dP instead.
+    // The scratch is a sequence of 16 KB tiles: per head of the group, per sequence, one tile per (128-key
+    // tile kt, 64-query tile qt >= 2 kt), key tile after key tile (tile kt * QT - kt * (kt - 1) + qt - 2 kt of
+    // its sequence, QT = 2 * key tiles of the sequence).  Inside a tile: [8 blocks of 8 queries][128 keys][8 bf16],
+    // the layout tcgen05 reads without a swizzle as an MN-major operand (8 keys x 16 bytes form a core matrix).
     CUtensorMap ds_map;       // the scratch as rows of 256 64-bit words (one 8-query block of a tile), boxes of 16 rows x 128 words
     __nv_bfloat16* ds_scratch;
-    int ds_pitch;             // the sequence length rounded up to 128
     int head0;
     const int* cu_seqlens;
     int batch;
@@ -106,9 +105,12 @@ static_assert(offsetof(BackwardBarriers, lse2) % 16 == 0 && offsetof(BackwardBar
 // blockIdx.z is the batch entry.  Packed: walk cu_seqlens.  Returns false when
 // the index is past the last block.
 __device__ __forceinline__ bool locate_block(const BackwardParams& p, int rows_per_block, int index, int& row0, int& length,
-                                             int& block, int& blocks_in_sequence, size_t& lse_offset, int head) {
+                                             int& block, int& blocks_in_sequence, size_t& lse_offset, int head, int* sequence_index = nullptr) {
     if (p.cu_seqlens == nullptr) {
         const int b = blockIdx.z;
+        if (sequence_index != nullptr) {
+            *sequence_index = b;
+        }
         row0 = b * p.max_seq;
         length = p.max_seq;
         blocks_in_sequence = (length + rows_per_block - 1) / rows_per_block;
@@ -121,6 +123,9 @@ __device__ __forceinline__ bool locate_block(const BackwardParams& p, int rows_p
         const int tokens = p.cu_seqlens[sequence + 1] - begin;
         const int blocks = (tokens + rows_per_block - 1) / rows_per_block;
         if (index < blocks) {
+            if (sequence_index != nullptr) {
+                *sequence_index = sequence;
+            }
             row0 = begin;
             length = tokens;
             block = index;
@@ -131,6 +136,34 @@ __device__ __forceinline__ bool locate_block(const BackwardParams& p, int rows_p
         index -= blocks;
     }
     return false;
+}
+
+// Where the dS^T tiles of `sequence` start inside one head's part of the scratch, how many tiles a head
+// has in all, and the sequence's number of 128-key tiles.
+struct ScratchPlace {
+    long long sequence_first;
+    long long head_tiles;
+    int key_tiles;
+};
+
+__device__ __forceinline__ ScratchPlace scratch_place(const BackwardParams& p, int sequence) {
+    ScratchPlace place = {0, 0, 0};
+    if (p.cu_seqlens == nullptr) {
+        const long long kt = (p.max_seq + BIG - 1) / BIG;
+        place.key_tiles = static_cast<int>(kt);
+        place.sequence_first = sequence * (kt * kt + kt);
+        place.head_tiles = p.batch * (kt * kt + kt);
+        return place;
+    }
+    for (int i = 0; i < p.batch; ++i) {
+        const long long kt = (p.cu_seqlens[i + 1] - p.cu_seqlens[i] + BIG - 1) / BIG;
+        if (i == sequence) {
+            place.sequence_first = place.head_tiles;
+            place.key_tiles = static_cast<int>(kt);
+        }
+        place.head_tiles += kt * kt + kt;
+    }
+    return place;
 }
 
 __device__ __forceinline__ void init_barriers(BackwardBarriers* bars, uint32_t stage_full_arrivals) {
@@ -594,9 +627,9 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
         return;
     }
     const int head = p.head0 + blockIdx.y;
-    int row0, length, block, blocks_in_sequence;
+    int row0, length, block, blocks_in_sequence, sequence;
     size_t lse_offset;
-    if (!locate_block(p, BIG, blockIdx.x, row0, length, block, blocks_in_sequence, lse_offset, head)) {
+    if (!locate_block(p, BIG, blockIdx.x, row0, length, block, blocks_in_sequence, lse_offset, head, &sequence)) {
         return;
     }
     const int key_start = block * BIG;                 // block 0 has the most queries: longest first
@@ -775,10 +808,10 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
         const int key_pos = key_start + r;
         uint4* ds_tiles = nullptr;             // this key tile's first tile of the scratch (query tile 2 * block)
         if (p.ds_scratch != nullptr) {
-            const size_t key_tiles = p.ds_pitch / BIG;
-            const size_t first = (static_cast<size_t>(blockIdx.z) * gridDim.y + blockIdx.y) * (key_tiles * key_tiles + key_tiles) +
-                                 static_cast<size_t>(block) * (2 * key_tiles) - static_cast<size_t>(block) * static_cast<size_t>(block > 0 ? block - 1 : 0);
-            ds_tiles = reinterpret_cast<uint4*>(p.ds_scratch) + first * (DS_TILE_BYTES / 16);
+            const ScratchPlace place = scratch_place(p, sequence);
+            const long long first = blockIdx.y * place.head_tiles + place.sequence_first + static_cast<long long>(block) * (2 * place.key_tiles) -
+                                    static_cast<long long>(block) * (block - 1);
+            ds_tiles = reinterpret_cast<uint4*>(p.ds_scratch) + static_cast<size_t>(first) * (DS_TILE_BYTES / 16);
         }
         bool alive = true;
         // Both groups work on every tile: thread = (key row, 32 of the tile's 64 queries), so a
@@ -957,16 +990,19 @@ __global__ void __launch_bounds__(dqs::STREAM_THREADS, 1) backward_dq_stream_ker
         return;
     }
     const int head = p.head0 + blockIdx.y;
-    const int length = p.max_seq;
-    const int row0 = blockIdx.z * p.max_seq;
-    const int q_tiles = (length + QROWS - 1) / QROWS;
-    const int q_start = (q_tiles - 1 - static_cast<int>(blockIdx.x)) * QROWS;        // longest first
+    int row0, length, block, blocks_in_sequence, sequence;
+    size_t lse_offset;
+    if (!locate_block(p, QROWS, blockIdx.x, row0, length, block, blocks_in_sequence, lse_offset, head, &sequence)) {
+        return;
+    }
+    const int q_start = (blocks_in_sequence - 1 - block) * QROWS;        // longest first
     const int key_end = min(length, q_start + QROWS);
     const int stage_count = (key_end + KSUB - 1) / KSUB;
     const bool second_used = q_start + 128 < length;
-    // rows of the scratch view (8-query blocks) before this (batch, head), and query tiles per key tile
-    const int key_tiles = p.ds_pitch / BIG;
-    const long long ds_row0 = static_cast<long long>(blockIdx.z * gridDim.y + blockIdx.y) * (key_tiles * key_tiles + key_tiles) * 8;
+    // rows of the scratch view (8-query blocks) before this (head, sequence), and key tiles of the sequence
+    const ScratchPlace place = scratch_place(p, sequence);
+    const int key_tiles = place.key_tiles;
+    const long long ds_row0 = (blockIdx.y * place.head_tiles + place.sequence_first) * 8;
     const int q_tile0 = q_start / SUB;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023U) & ~1023U;
@@ -1122,26 +1158,25 @@ std::size_t parts_bytes(int total_tokens, int heads) {
     return (static_cast<std::size_t>(total_tokens) * heads * 64 * sizeof(float) + 255) / 256 * 256;
 }
 
-// Dense batches keep dS^T of a group of heads in scratch between the two main kernels.  The
-// group is as many heads as fit in ds_scratch_limit (20 GiB unless the caller sets another); 0 = not even one head fits (or the batch
-// is packed), and the backward recomputes S and dP in a dQ kernel of its own instead.
+// dS^T of a group of heads stays in scratch between the two main kernels.  The group is as many heads as
+// fit in ds_scratch_limit (20 GiB unless the caller sets another); 0 = not even one head fits, and the
+// backward recomputes S and dP in a dQ kernel of its own instead.
 std::atomic<std::size_t> ds_scratch_limit{std::size_t{20} << 30};
 
-int ds_pitch(int max_sequence_length) {
-    return (max_sequence_length + 127) / 128 * 128;
-}
-
-// 16 KB tiles of dS^T per (batch, head): key tile kt keeps its query tiles 2 kt .. QT - 1
-std::size_t ds_tiles_per_head(int max_sequence_length) {
-    const std::size_t key_tiles = static_cast<std::size_t>(ds_pitch(max_sequence_length)) / BIG;
-    return key_tiles * key_tiles + key_tiles;
+// An upper bound, computable without the lengths, on the 16 KB tiles of dS^T one head needs: a sequence of
+// k key tiles takes k * k + k.  Every sequence is at most max_sequence_length long (first bound) and the
+// squares of the lengths add up to at most max_sequence_length * total_tokens (second bound; k <=
+// length / 128 + 1).  Dense batches meet the first bound exactly.
+std::size_t ds_tiles_per_head(int batch_size, int max_sequence_length, int total_tokens) {
+    const std::size_t key_tiles = (static_cast<std::size_t>(max_sequence_length) + BIG - 1) / BIG;
+    const std::size_t by_longest = static_cast<std::size_t>(batch_size) * (key_tiles * key_tiles + key_tiles);
+    const std::size_t by_total = static_cast<std::size_t>(max_sequence_length) * static_cast<std::size_t>(total_tokens) / (BIG * BIG) + 1 +
+                                 3 * static_cast<std::size_t>(total_tokens) / BIG + 1 + 2 * static_cast<std::size_t>(batch_size);
+    return by_longest < by_total ? by_longest : by_total;
 }
 
 int ds_group_heads(int batch_size, int max_sequence_length, int total_tokens, int heads) {
-    if (static_cast<long long>(batch_size) * max_sequence_length != total_tokens) {
-        return 0;
-    }
-    const std::size_t per_head = static_cast<std::size_t>(batch_size) * ds_tiles_per_head(max_sequence_length) * DS_TILE_BYTES;
+    const std::size_t per_head = ds_tiles_per_head(batch_size, max_sequence_length, total_tokens) * DS_TILE_BYTES;
     const std::size_t fit = ds_scratch_limit.load() / per_head;
     return static_cast<int>(fit < static_cast<std::size_t>(heads) ? fit : static_cast<std::size_t>(heads));
 }
@@ -1168,8 +1203,9 @@ std::size_t mla_prefill_backward_scratch_limit(long long bytes) {
 }
 
 int mla_prefill_backward_launches(int batch_size, int max_sequence_length, int total_tokens, int heads, bool packed) {
-    const int group = packed ? 0 : ds_group_heads(batch_size, max_sequence_length, total_tokens, heads);
-    // delta, the two main kernels (once per group of heads on the dense path), the dk_pe sum
+    (void)packed;       // dense and packed batches take the same route
+    const int group = ds_group_heads(batch_size, max_sequence_length, total_tokens, heads);
+    // delta, the two main kernels (once per group of heads), the dk_pe sum
     return group > 0 ? 2 + 2 * ((heads + group - 1) / group) : 4;
 }
 
@@ -1178,9 +1214,9 @@ std::size_t mla_prefill_backward_workspace_bytes(int batch_size, int max_sequenc
         return 0;
     }
     // dk_pe sums, then delta [tokens, heads], then the per-head dk_pe contributions [tokens, heads, 64],
-    // then (dense batches) dS^T of one group of heads
-    const std::size_t scratch = static_cast<std::size_t>(ds_group_heads(batch_size, max_sequence_length, total_tokens, heads)) * batch_size *
-                                ds_tiles_per_head(max_sequence_length) * DS_TILE_BYTES;
+    // then dS^T of one group of heads
+    const std::size_t scratch = static_cast<std::size_t>(ds_group_heads(batch_size, max_sequence_length, total_tokens, heads)) *
+                                ds_tiles_per_head(batch_size, max_sequence_length, total_tokens) * DS_TILE_BYTES;
     return accumulator_bytes(total_tokens) + delta_bytes(total_tokens, heads) + parts_bytes(total_tokens, heads) + scratch;
 }
 
@@ -1242,22 +1278,29 @@ void mla_prefill_backward_cuda(__nv_bfloat16* dq, __nv_bfloat16* dk_nope, __nv_b
     delta_kernel<<<delta_blocks, 256, 0, stream>>>(delta, output_gradient, output, cu_seqlens, batch_size, max_sequence_length, total_tokens, heads);
     CUDA_CHECK(cudaGetLastError());
 
-    const int group = cu_seqlens == nullptr ? ds_group_heads(batch_size, max_sequence_length, total_tokens, heads) : 0;
+    const int group = ds_group_heads(batch_size, max_sequence_length, total_tokens, heads);
     if (group > 0) {
-        // dense: per group of heads, the key-side kernel (which leaves dS^T in the scratch) and then dQ from it
-        const int pitch = ds_pitch(max_sequence_length);
+        // per group of heads: the key-side kernel (which leaves dS^T in the scratch) and then dQ from it
         params.ds_scratch = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(workspace) + accumulator_bytes(total_tokens) + delta_bytes(total_tokens, heads) +
                                                              parts_bytes(total_tokens, heads));
-        params.ds_pitch = pitch;
-        params.ds_map = make_u64_rows_map(params.ds_scratch, static_cast<std::uint64_t>(batch_size) * group * ds_tiles_per_head(max_sequence_length) * 8, 256,
-                                          128, 16);
+        params.ds_map = make_u64_rows_map(params.ds_scratch, static_cast<std::uint64_t>(group) * ds_tiles_per_head(batch_size, max_sequence_length, total_tokens) * 8,
+                                          256, 128, 16);
+        dim3 key_grid, query_grid;
+        if (cu_seqlens == nullptr) {
+            key_grid = dim3((max_sequence_length + BIG - 1) / BIG, 1, batch_size);
+            query_grid = dim3((max_sequence_length + dqs::QROWS - 1) / dqs::QROWS, 1, batch_size);
+        } else {
+            key_grid = dim3(total_tokens / BIG + batch_size, 1, 1);
+            query_grid = dim3(total_tokens / dqs::QROWS + batch_size, 1, 1);
+        }
         for (int head0 = 0; head0 < heads; head0 += group) {
             const int count = heads - head0 < group ? heads - head0 : group;
             params.head0 = head0;
-            backward_dkdv_kernel<<<dim3((max_sequence_length + BIG - 1) / BIG, count, batch_size), THREADS, SMEM_BYTES, stream>>>(params);
+            key_grid.y = count;
+            query_grid.y = count;
+            backward_dkdv_kernel<<<key_grid, THREADS, SMEM_BYTES, stream>>>(params);
             CUDA_CHECK(cudaGetLastError());
-            backward_dq_stream_kernel<<<dim3((max_sequence_length + dqs::QROWS - 1) / dqs::QROWS, count, batch_size), dqs::STREAM_THREADS, dqs::STREAM_SMEM_BYTES, stream>>>(
-                params);
+            backward_dq_stream_kernel<<<query_grid, dqs::STREAM_THREADS, dqs::STREAM_SMEM_BYTES, stream>>>(params);
             CUDA_CHECK(cudaGetLastError());
         }
     } else {

@@ -200,17 +200,19 @@ void mla_prefill_forward_cuda(
     float scale,
     cudaStream_t stream = nullptr);
 
-// Dense batches (total_tokens == batch_size * max_sequence_length, cu_seqlens null) run the backward
-// as: key-side kernel (dK, dV, and dS^T of a group of heads left in the workspace), then dQ = dS K
-// streamed from there, group after group; nothing is recomputed, at the price of workspace:
-// 2 bytes per causal (query, key) pair and head of a group, 128-row tiles.  A group is as many heads
-// as fit in the limit set here (default 20 GiB; the call returns the previous limit, a negative
-// value only reads it).  When not even one head fits, and for packed batches, dQ comes from a kernel
-// that recomputes S and dP instead and the workspace is small.  Set the limit before asking for the
-// workspace size and keep it unchanged until the backward call that uses that workspace.
+// The backward runs as: key-side kernel (dK, dV, and dS^T of a group of heads left in the workspace), then
+// dQ = dS K streamed from there, group after group; nothing is recomputed, at the price of workspace:
+// 2 bytes per causal (query, key) pair and head of a group, in 128 x 64 tiles.  The workspace size is a
+// bound that needs no lengths (every sequence at most max_sequence_length long, squares of the lengths
+// at most max_sequence_length * total_tokens in sum); dense batches meet it exactly.  A group is as many
+// heads as fit in the limit set here (default 20 GiB; the call returns the previous limit, a negative
+// value only reads it).  When not even one head fits, dQ comes from a kernel that recomputes S and dP
+// instead and the workspace is small.  Set the limit before asking for the workspace size and keep it
+// unchanged until the backward call that uses that workspace.
 std::size_t mla_prefill_backward_scratch_limit(long long bytes);
 
-// Kernels one mla_prefill_backward_cuda call launches for this shape (packed: cu_seqlens non-null).
+// Kernels one mla_prefill_backward_cuda call launches for this shape (`packed` is ignored: dense and
+// packed batches take the same route).
 int mla_prefill_backward_launches(int batch_size, int max_sequence_length, int total_tokens, int heads, bool packed);
 
 // Bytes of caller-owned device scratch the backward needs.

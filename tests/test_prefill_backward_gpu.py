@@ -181,7 +181,6 @@ def test_dense_backward_paths_agree(gpu, limit_heads):
     try:
         expected_launches = 4 if limit_heads == 0 else 2 + 2 * ((h + limit_heads - 1) // limit_heads)
         assert mla.prefill_backward_launches(b, s, b * s, h) == expected_launches
-        assert mla.prefill_backward_launches(b, s, b * s, h, packed=True) == 4
         grads = mla.prefill_backward(dout.to(gpu), out, lse, *device, SCALE)
         torch.cuda.synchronize()
         assert mla.device_status() == 0
@@ -189,3 +188,23 @@ def test_dense_backward_paths_agree(gpu, limit_heads):
         mla.prefill_backward_scratch_limit(previous)
     assert mla.prefill_backward_scratch_limit() == previous
     check_grads(tuple(g.cpu() for g in grads), oracle.prefill_backward(dout, out.cpu(), lse.cpu(), *tensors, SCALE))
+
+
+@pytest.mark.parametrize("limit", [None, 0, 1 << 20])
+def test_packed_backward_routes_agree(gpu, limit):
+    """Packed batches: dQ streamed from the stored dS^T (default limit: one group; 1 MiB: one head per group, the
+    workspace sized by the bound that needs no lengths) and the recomputing kernel (limit 0) against the oracle."""
+    from dscuda_b200 import mla
+    seqlens = [70, 1, 333, 128, 200]
+    heads = 3
+    total = sum(seqlens)
+    q_nope, q_pe, k_nope, k_pe, v, dout, cu = oracle.prefill_inputs(17, 0, 0, heads, dout_std=0.1, seqlens=seqlens)
+    tensors = (q_nope, q_pe, k_nope, k_pe, v)
+    previous = mla.prefill_backward_scratch_limit(-1 if limit is None else limit)
+    try:
+        launches = mla.prefill_backward_launches(len(seqlens), max(seqlens), total, heads, packed=True)
+        assert launches == {None: 4, 0: 4, 1 << 20: 8}[limit]
+        out, lse, grads = run_backward(gpu, tensors, dout, SCALE, cu, max(seqlens))
+    finally:
+        mla.prefill_backward_scratch_limit(previous)
+    check_grads(grads, oracle.prefill_backward(dout, out, lse, *tensors, SCALE, cu))
