@@ -888,7 +888,8 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
                 uint4* dst = ds_tiles + static_cast<size_t>(t) * (DS_TILE_BYTES / 16) + (group * 4) * BIG + r;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    dst[e * BIG] = key_pos < length ? make_uint4(packed[4 * e], packed[4 * e + 1], packed[4 * e + 2], packed[4 * e + 3]) : make_uint4(0, 0, 0, 0);
+                    const uint4 value = key_pos < length ? make_uint4(packed[4 * e], packed[4 * e + 1], packed[4 * e + 2], packed[4 * e + 3]) : make_uint4(0, 0, 0, 0);
+                    __stcs(dst + e * BIG, value);       // written once, read once by the next kernel: streaming store
                 }
             }
         }
