@@ -248,7 +248,7 @@ def run_ours(args, rank, world, device):
                 "config": {"workload": f"decode only: batch {args.decode_batch}, heads 128, lengths uniform in [1024, 32768], seed 3"},
                 "gpu_launches": 2 * args.steps, "roofline": decode["roofline"], "decode": decode} if rank == 0 else None
     numa = bind_to_gpu_numa_node(device.index)
-    x = workloads.dense_inputs(w, device, shard=rank)
+    x = workloads.dense_inputs(w, device, shard=rank, rotate=mla.rope_apply)
     fwd_in = (x["q_nope"], x["q_pe"], x["k_nope"], x["k_pe"], x["v"])
     out = torch.empty_like(x["v"])
     lse = torch.empty(w["batch"], w["heads"], w["seq"], device=device)
@@ -387,7 +387,7 @@ def run_ours(args, rank, world, device):
 def bench_prefill(mla, checks, device, peaks, rank, barrier, reduce_max, steps=10, warmup=3, verify=True):
     """Causal forward alone at B=4, S=4096, H=128 per GPU (the prefill configuration)."""
     w = workloads.CONFIGS["C2"]
-    x = workloads.dense_inputs(w, device, shard=rank)
+    x = workloads.dense_inputs(w, device, shard=rank, rotate=mla.rope_apply)
     fwd_in = (x["q_nope"], x["q_pe"], x["k_nope"], x["k_pe"], x["v"])
     out = torch.empty_like(x["v"])
     lse = torch.empty(w["batch"], w["heads"], w["seq"], device=device)
@@ -443,7 +443,7 @@ def bench_varlen(mla, device, peaks, rank, world, barrier, reduce_max, heads=16,
     [512, 32768], 121 320 tokens), 16 heads per GPU (each rank its own 16 heads of the 128-head job)."""
     lengths = workloads.varlen_lengths()
     total = sum(lengths)
-    tensors, cu = workloads.packed_inputs(lengths, heads, 4, device, shard=rank)
+    tensors, cu = workloads.packed_inputs(lengths, heads, 4, device, shard=rank, rotate=mla.rope_apply)
     x = (tensors["q_nope"], tensors["q_pe"], tensors["k_nope"], tensors["k_pe"], tensors["v"])
     dout = tensors["dout"]
     out = torch.empty_like(x[4])

@@ -126,7 +126,7 @@ class Case:
 
 
 def dense_case(name: str, config: dict, device: torch.device, operation: Optional[str], shard: int, world: int) -> Case:
-    x = workloads.dense_inputs(config, device, shard=shard)
+    x = workloads.dense_inputs(config, device, shard=shard, rotate=mla.rope_apply)
     ins = (x["q_nope"], x["q_pe"], x["k_nope"], x["k_pe"], x["v"])
     out = torch.empty_like(x["v"])
     lse = torch.empty(config["batch"], config["heads"], config["seq"], device=device)
@@ -162,7 +162,7 @@ def dense_case(name: str, config: dict, device: torch.device, operation: Optiona
 
 def packed_case(name: str, config: dict, device: torch.device, operation: Optional[str], shard: int, world: int) -> Case:
     lengths = workloads.varlen_lengths(config["seed"], config["sequences"], config["low"], config["high"])
-    x, cu = workloads.packed_inputs(lengths, config["heads"], config["seed"], device, config["dout_std"], shard=shard)
+    x, cu = workloads.packed_inputs(lengths, config["heads"], config["seed"], device, config["dout_std"], shard=shard, rotate=mla.rope_apply)
     ins = (x["q_nope"], x["q_pe"], x["k_nope"], x["k_pe"], x["v"])
     total, longest = sum(lengths), max(lengths)
     out = torch.empty_like(x["v"])

@@ -54,11 +54,12 @@ def decode_flops(lengths: torch.Tensor, heads: int) -> int:
     return 2 * (576 + 512) * heads * int(lengths.sum())
 
 
-def dense_inputs(config: dict, device: torch.device, shard: int = 0) -> Dict[str, torch.Tensor]:
-    """Seeded N(0,1) bf16 tensors drawn on the device.  Rotary embedding is input preparation:
-    the kernels take q_pe / k_pe as they are.  `shard` selects the per-head tensors of one head
-    shard of a larger job (a different stream of draws per shard); `k_pe`, the rotary key every head
-    shares, is the same for every shard."""
+def dense_inputs(config: dict, device: torch.device, shard: int = 0, rotate=None) -> Dict[str, torch.Tensor]:
+    """Seeded N(0,1) bf16 tensors drawn on the device.  Rotary embedding is input preparation (the
+    kernels take q_pe / k_pe as they are): `rotate(q_pe, k_pe, positions)`, when given, applies it in place
+    with position = index along the sequence (`dscuda_b200.mla.rope_apply` has that signature).  `shard`
+    selects the per-head tensors of one head shard of a larger job (a different stream of draws per
+    shard); `k_pe`, the rotary key every head shares, is the same for every shard."""
     shared = torch.Generator(device=device).manual_seed(config["seed"])
     g = torch.Generator(device=device).manual_seed(config["seed"] + 7919 * shard) if shard else shared
     b, s, h = config["batch"], config["seq"], config["heads"]
@@ -70,6 +71,8 @@ def dense_inputs(config: dict, device: torch.device, shard: int = 0) -> Dict[str
     tensors = dict(q_nope=draw(b, s, h, 128), q_pe=draw(b, s, h, 64), k_nope=draw(b, s, h, 128), k_pe=k_pe, v=draw(b, s, h, 128))
     if config["backward"]:
         tensors["dout"] = draw(b, s, h, 128, std=config["dout_std"])
+    if rotate is not None:
+        rotate(tensors["q_pe"], tensors["k_pe"], None)
     return tensors
 
 
@@ -80,8 +83,9 @@ def varlen_lengths(seed: int = 4, count: int = 16, low: int = 512, high: int = 3
     return [int(round(math.exp(math.log(low) + float(x) * (math.log(high) - math.log(low))))) for x in u]
 
 
-def packed_inputs(lengths: List[int], heads: int, seed: int, device: torch.device, dout_std: float = 0.1, shard: int = 0):
-    """Packed [total, H, *] tensors plus int32 cu_seqlens on the device (`shard` as in dense_inputs)."""
+def packed_inputs(lengths: List[int], heads: int, seed: int, device: torch.device, dout_std: float = 0.1, shard: int = 0, rotate=None):
+    """Packed [total, H, *] tensors plus int32 cu_seqlens on the device (`shard` and `rotate` as in
+    dense_inputs; positions restart at 0 in every sequence)."""
     total = sum(lengths)
     shared = torch.Generator(device=device).manual_seed(seed)
     g = torch.Generator(device=device).manual_seed(seed + 7919 * shard) if shard else shared
@@ -94,6 +98,9 @@ def packed_inputs(lengths: List[int], heads: int, seed: int, device: torch.devic
                    v=draw(total, heads, 128))
     tensors["dout"] = draw(total, heads, 128, std=dout_std)
     cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=device)
+    if rotate is not None:
+        positions = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths]).to(device)
+        rotate(tensors["q_pe"], tensors["k_pe"], positions)
     return tensors, cu
 
 
