@@ -23,7 +23,6 @@ void launch_prefill_forward(__nv_bfloat16* output, float* logsumexp, const __nv_
 
 // Per-translation-unit sticky status words (0 = fine).  Reading synchronises.
 int forward_device_status(bool reset);
-int absorbed_device_status(bool reset);
 int absorbed_backward_device_status(bool reset);
 int decode_device_status(bool reset);
 int projection_device_status(bool reset);

@@ -37,13 +37,12 @@ void check_prefill_shape(const int* cu_seqlens, int batch_size, int max_sequence
 
 int mla_device_status(bool reset) {
     const int forward = internal::forward_device_status(reset);
-    const int absorbed = internal::absorbed_device_status(reset);
     const int absorbed_backward = internal::absorbed_backward_device_status(reset);
     const int decode = internal::decode_device_status(reset);
     const int projection = internal::projection_device_status(reset);
     const int backward = internal::backward_device_status(reset);
     const int append = internal::append_device_status(reset);
-    for (const int status : {forward, absorbed, decode, absorbed_backward, backward, projection}) {
+    for (const int status : {forward, decode, absorbed_backward, backward, projection}) {
         if (status != 0) {
             return status;
         }
