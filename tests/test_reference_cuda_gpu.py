@@ -19,6 +19,7 @@ pytestmark = pytest.mark.gpu
 
 ROOT = pathlib.Path(__file__).resolve().parents[1]
 REFERENCE_LIBRARY = ROOT / "oracle" / "_ref" / "libdscuda_mla_reference.so"
+FLASH_REFERENCE_LIBRARY = ROOT / "oracle" / "_ref" / "libdscuda_flash_attention_reference.so"
 P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
 
@@ -148,6 +149,16 @@ def test_speed_beside_the_reference_kernels(gpu, reference):
             microseconds(lambda: reference.dscuda_mla_decode(r_out.data_ptr(), r_lse.data_ptr(), query.data_ptr(), cache.data_ptr(), table.data_ptr(),
                                                              lengths.data_ptr(), workspace.data_ptr(), b, h, 512, 64, 64, pages, 8, scale, stream())))
         torch.testing.assert_close(d_out.float(), r_out.float(), atol=8e-3, rtol=8e-3)
+    if FLASH_REFERENCE_LIBRARY.exists():        # the largest shape of the reference's flash-attention list
+        flash = ctypes.CDLL(str(FLASH_REFERENCE_LIBRARY))
+        flash.dscuda_flash_forward.argtypes = [P] * 5 + [I] * 5 + [F, P]
+        b, t, hq, hkv = 4, 2048, 8, 1
+        fq, fk, fv = draw(b, t, hq, 128), draw(b, t, hkv, 128), draw(b, t, hkv, 128)
+        f_out, f_lse = torch.empty_like(fq), torch.empty(b, hq, t, device=gpu)
+        rows[f"flash forward B={b} T={t} Hq={hq} Hkv={hkv}"] = (
+            microseconds(lambda: mla.flash_forward(fq, fk, fv, 128 ** -0.5)),
+            microseconds(lambda: flash.dscuda_flash_forward(f_out.data_ptr(), f_lse.data_ptr(), fq.data_ptr(), fk.data_ptr(), fv.data_ptr(),
+                                                            b, t, hq, hkv, 128, 128 ** -0.5, stream())))
     report = {name: {"this_us": mine, "reference_us": theirs, "speedup": theirs / mine} for name, (mine, theirs) in rows.items()}
     for name, row in report.items():
         print(f"{name}: this {row['this_us']:.1f} us, reference kernels {row['reference_us']:.1f} us, x{row['speedup']:.1f}")
@@ -155,3 +166,28 @@ def test_speed_beside_the_reference_kernels(gpu, reference):
     if log.is_dir():
         (log / "reference_cuda_timing.json").write_text(json.dumps(report, indent=1))
     assert all(row["speedup"] >= 1.0 for row in report.values()), report
+
+
+@pytest.mark.parametrize("b,t,hq,hkv", [(1, 64, 2, 2), (2, 64, 4, 2), (1, 128, 4, 1), (1, 256, 8, 8), (1, 512, 8, 2), (4, 2048, 8, 1)])
+def test_flash_forward_equals_the_reference_kernel(gpu, b, t, hq, hkv):
+    """D = 128 grouped-query forward on the shapes of `benchmarks/flash_attention.py:42-56` of the reference (input
+    scale 0.5, tolerances of its own check), both libraries timed on the largest one."""
+    from dscuda_b200 import mla
+    if not FLASH_REFERENCE_LIBRARY.exists():
+        pytest.skip("the reference's CUDA kernels were not built (python oracle/build_reference_cuda.py)")
+    lib = ctypes.CDLL(str(FLASH_REFERENCE_LIBRARY))
+    lib.dscuda_flash_forward.argtypes = [P] * 5 + [I] * 5 + [F, P]
+    lib.dscuda_flash_last_error.restype = ctypes.c_char_p
+    g = torch.Generator().manual_seed(t + hq)
+    q = (torch.randn(b, t, hq, 128, generator=g) * 0.5).bfloat16().to(gpu)
+    k = (torch.randn(b, t, hkv, 128, generator=g) * 0.5).bfloat16().to(gpu)
+    v = (torch.randn(b, t, hkv, 128, generator=g) * 0.5).bfloat16().to(gpu)
+    scale = 128 ** -0.5
+    ref_out = torch.empty_like(q)
+    ref_lse = torch.empty(b, hq, t, device=gpu)
+    status = lib.dscuda_flash_forward(ref_out.data_ptr(), ref_lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), b, t, hq, hkv, 128, scale, stream())
+    assert status == 0, lib.dscuda_flash_last_error().decode()
+    out, lse = mla.flash_forward(q, k, v, scale)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.float(), ref_out.float(), atol=1e-2, rtol=1e-2)
+    torch.testing.assert_close(lse, ref_lse, atol=1e-4, rtol=1e-4)
