@@ -1,27 +1,32 @@
 // Backward of the non-absorbed causal MLA attention for sm_100a.
 //
 // One call launches, on the caller's stream:
-//   1. delta_kernel:        delta[q] = sum_d dO[q,d] * O[q,d]            (fp32, LSE layout);
-//   2. backward_dq_kernel:  per 128-row query tile, over 128-key tiles
-//                           S = Q K^T, dP = dO V^T (tcgen05, fp32 in tensor memory, dO as a
-//                           tensor-memory operand), P = exp(S*scale - LSE),
-//                           dS = P (dP - delta) scale (registers, in two stages),
-//                           dQ += dS K with dS fed from tensor memory;
-//   3. backward_dkdv_kernel: per 128-key tile, over 64-query tiles
-//                           S^T = K Q^T, dP^T = V dO^T, P^T, dS^T as above (one thread per key),
-//                           dV += P^T dO, dK += dS^T Q; the rotary 64 columns of dK go, per head
-//                           and in fp32, to the workspace;
-//   4. sum_dk_pe_kernel:    those contributions added over the heads in index order -> the fp32
-//                           sums at the start of the workspace and bf16 dk_pe.
+//   1. delta_kernel:          delta[q] = sum_d dO[q,d] * O[q,d]            (fp32, LSE layout);
+//   then, for one group of heads after the other (as many heads as the dS scratch holds),
+//   2. backward_dkdv_kernel:  per 128-key tile, over 64-query tiles
+//                             S^T = K Q^T, dP^T = V dO^T (tcgen05, fp32 in tensor memory),
+//                             P^T = exp(S^T*scale - LSE), dS^T = P^T (dP^T - delta) scale (one thread
+//                             per key, bf16 back into tensor memory as the A operands),
+//                             dV += P^T dO, dK += dS^T Q; the rotary 64 columns of dK go, per head
+//                             and in fp32, to the workspace; dS^T goes to the scratch as well;
+//   3. backward_dq_stream_kernel: per 256 query rows, dQ = dS K streamed from the scratch: nothing is
+//                             recomputed, the kernel is bound by reading dS once from HBM;
+//   and finally
+//   4. sum_dk_pe_kernel:      the per-head dk_pe contributions added in head order -> the fp32 sums
+//                             at the start of the workspace and bf16 dk_pe.
 //
-// S and dP are recomputed in both main kernels: a 128x192 dQ tile, a 128x192 dK
-// tile and a 128x128 dV tile plus the score tiles do not fit the 512 tensor
-// memory columns of one SM together, and splitting keeps every gradient a plain
-// single-writer store: results are bit-identical from call to call.
+// A single fused kernel does not fit: dV (128) + dK (192) + the score tiles fill the 512 tensor-memory
+// columns, so a dQ accumulator has no room, and adding dQ partials into global memory instead costs
+// more than writing dS once and reading it back (measured; see build/probe_dq_reduction).  Every
+// gradient is a plain single-writer store, so results are bit-identical from call to call.
 //
-// Both main kernels: warps 0-7 are the softmax threads (all 256 on the same tile,
-// two per row), warp 8 issues the MMAs (the whole warp runs the loop, one elected
-// lane executes the instruction), warp 9 loads with TMA.  Every wait is bounded.
+// When the caller leaves no room for the scratch (mla_prefill_backward_scratch_limit), step 2 runs
+// without the dS output and backward_dq_kernel takes the place of step 3: per 128-row query tile it
+// recomputes S = Q K^T and dP = dO V^T over 128-key tiles and accumulates dQ += dS K.
+//
+// Key-side and recomputing kernels: warps 0-7 are the softmax threads (all 256 on the same tile,
+// two per row), warp 8 issues the MMAs (the whole warp runs the loop, one elected lane executes the
+// instruction), warp 9 loads with TMA.  Every wait is bounded.
 #include "mla.h"
 #include "cuda_common.h"
 #include "attention_internal.h"
@@ -949,7 +954,7 @@ __global__ void __launch_bounds__(THREADS, 1) backward_dkdv_kernel(const __grid_
 }
 
 // ---------------------------------------------------------------------------
-// dQ from stored dS (dense batches): dQ[q, :] = sum over keys <= q of dS[q, key] * K[key, :].
+// dQ from stored dS: dQ[q, :] = sum over keys <= q of dS[q, key] * K[key, :].
 //
 // backward_dkdv_kernel has written dS^T (scale included, zeros above the diagonal) to the
 // scratch, so this is a causal batched GEMM with nothing to recompute: 384 FLOP per (query,
