@@ -410,6 +410,10 @@ def bench_decode(mla, checks, sharding, device, peaks, rank, world, barrier, red
     mine = sharding.decode_partition(lengths.tolist(), world)[rank] if world > 1 else list(range(batch))
     query, table, lengths = query[mine].contiguous(), table[mine].contiguous(), lengths[mine].contiguous()
     total_tokens = int(lengths.sum())
+    if world > 1:
+        # a rank's share is a small batch of long sequences: more partial slots than the harness's 8, so that the
+        # kernel can still hand every pair of SMs an equal range of tiles
+        splits = mla.decode_splits(lengths.tolist(), 128, minimum=splits)
     q, c, t, n = (z.to(device) for z in (query, cache, table, lengths))
     local = len(mine)
     workspace = mla.decode_workspace(local, 128, splits, 512, device)

@@ -78,6 +78,17 @@ def decode_workspace(batch, heads, splits, rank=512, device="cuda"):
     return torch.empty(lib.dscuda_mla_workspace_elements(batch, heads, splits, rank), device=device, dtype=torch.float32)
 
 
+def decode_splits(lengths, heads=128, minimum=8, clusters=74, maximum=64) -> int:
+    """Partial slots per (sequence, head) that let the decode kernel cut the batch's 128-key tiles into equal ranges,
+    one per pair of SMs.  The kernel never makes a range shorter than longest sequence / (splits - 1) tiles (a sequence
+    may not spread over more ranges than it has slots), so a small batch of long sequences needs more slots than the
+    reference harness's 8 to keep every SM pair busy.  `lengths`: cached tokens per sequence (a list or a CPU tensor)."""
+    tiles = [(int(n) + 127) // 128 for n in lengths]
+    head_tiles = (heads + 127) // 128
+    per_range = max(1, -(-sum(tiles) * head_tiles // clusters))
+    return max(minimum, min(maximum, 1 + -(-max(tiles, default=1) // per_range)))
+
+
 def mla_decode(query, paged_cache, block_table, lengths, scale, splits=8, workspace=None, output=None, lse=None, checked_pages=False):
     """Paged decode (`dscuda_mla_decode`; `dscuda_mla_decode_checked` with `checked_pages`, which also
     passes the number of cache pages so that a page number outside the cache is replaced and reported).

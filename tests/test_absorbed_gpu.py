@@ -53,7 +53,8 @@ def test_decode_matches_reference_fixture(gpu, name, splits):
     torch.testing.assert_close(lse.cpu(), g["lse"], atol=1e-4, rtol=1e-4)
 
 
-@pytest.mark.parametrize("batch,heads,low,high,splits", [(3, 128, 1, 700, 4), (5, 16, 60, 2000, 8), (2, 200, 500, 1500, 3)])
+@pytest.mark.parametrize("batch,heads,low,high,splits", [(3, 128, 1, 700, 4), (5, 16, 60, 2000, 8), (2, 200, 500, 1500, 3), (2, 128, 6000, 9000, 17),
+                                                        (1, 128, 12000, 12001, 40)])
 def test_decode_permuted_pages_and_garbage_tail(gpu, batch, heads, low, high, splits):
     """Random page permutation; the unused tail of every last page and all unused
     pages are filled with NaN, which must not reach the output."""

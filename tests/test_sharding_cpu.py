@@ -75,3 +75,14 @@ def test_head_sharded_forward_backward_on_two_gloo_ranks():
     results = manager.dict()
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
     assert dict(results) == {0: "ok", 1: "ok"}
+
+
+def test_decode_splits_keep_the_ranges_equal():
+    """`mla.decode_splits`: enough partial slots that the longest sequence may spread over ranges of total / 74 tiles,
+    never fewer than the reference harness's 8, never more than 64."""
+    from dscuda_b200 import mla
+    assert mla.decode_splits([1024] * 64) == 8                       # many short sequences: the minimum
+    lengths = [32768] * 8                                            # 8 x 256 tiles: 28 per range, a sequence spans 10 ranges
+    assert mla.decode_splits(lengths) == 1 + -(-256 // -(-8 * 256 // 74))
+    assert mla.decode_splits([32768]) == 64                          # one sequence over all 74 ranges: capped
+    assert mla.decode_splits([5], heads=16) == 8
