@@ -44,6 +44,34 @@ def test_workspace_sizes_are_host_only():
     assert lib.dscuda_mla_prefill_backward_workspace_bytes(2, 8192, 16384, 128) >= 16384 * 64 * 4 + 16384 * 128 * 4
 
 
+def test_backward_workspace_follows_the_scratch_limit():
+    """Host-only arithmetic of the backward's dS^T scratch: 16 KB per (128-key tile, 64-query tile at or after it), as many
+    heads at a time as the limit holds, the recomputing route (small workspace, four launches) when not even one fits."""
+    lib = library.library("mla")
+    batch, seq, heads = 2, 8192, 128
+    fixed = 16384 * 64 * 4 + 16384 * heads * 4 + 16384 * heads * 64 * 4          # dk_pe sums, delta, per-head dk_pe contributions
+    key_tiles = seq // 128
+    per_head = batch * (key_tiles * key_tiles + key_tiles) * 16384              # 2 bytes per causal pair, tile-rounded
+    previous = lib.dscuda_mla_prefill_backward_scratch_limit(-1)
+    try:
+        assert lib.dscuda_mla_prefill_backward_scratch_limit(-1) == previous                       # a negative value only reads
+        for limit, group in ((0, 0), (per_head - 1, 0), (per_head, 1), (5 * per_head + 7, 5), (1 << 40, heads)):
+            lib.dscuda_mla_prefill_backward_scratch_limit(limit)
+            size = lib.dscuda_mla_prefill_backward_workspace_bytes(batch, seq, batch * seq, heads)
+            assert fixed + group * per_head <= size <= fixed + group * per_head + 4096, (limit, group)
+            launches = lib.dscuda_mla_prefill_backward_launches(batch, seq, batch * seq, heads, 0)
+            assert launches == (4 if group == 0 else 2 + 2 * -(-heads // group))
+        # packed batches: the bound needs no lengths and is never above the dense figure for the same longest sequence
+        lib.dscuda_mla_prefill_backward_scratch_limit(1 << 40)
+        packed = lib.dscuda_mla_prefill_backward_workspace_bytes(16, 32768, 121320, 16)
+        tokens_fixed = 121320 * 64 * 4 + 121320 * 16 * 4 + 121320 * 16 * 64 * 4
+        assert packed - tokens_fixed <= 16 * (32768 * 121320 + 4 * 121320 * 128 + 64 * 16384) + 8192
+        assert packed - tokens_fixed >= 16 * sum(n * n for n in (25869, 26465)) + 0          # at least what its two longest sequences need
+    finally:
+        lib.dscuda_mla_prefill_backward_scratch_limit(previous)
+    assert lib.dscuda_mla_prefill_backward_scratch_limit(-1) == previous
+
+
 @pytest.mark.parametrize("rank,rope", [(256, 64), (512, 32)])
 def test_absorbed_entry_points_reject_other_head_sizes(rank, rope):
     lib = library.library("mla")
