@@ -15,13 +15,13 @@ HBM.  `e2e` is the same metric through the host-buffer API: pinned host inputs
 copied to the device and the result read back inside the timed region.  The
 `decode` object reports the absorbed paged decode (batch 64, lengths uniform in
 [1024, 32768], 64-token pages, permuted page table) in GB/s of algorithmic
-bytes.  With several GPUs every rank runs the same per-GPU shard (heads are
-independent), there is no collective on the data path, and the job value is the
-sum over ranks divided by the slowest rank's time.
+bytes.  There is no collective on the data path, and the job value is the sum
+over ranks divided by the slowest rank's time.
 
 With N > 1 GPUs the job is the head-sharded one: every rank owns its own 128 heads of an
 H = 128*N job (its own draws; the shared rotary key is the same everywhere), the decode
-benchmark's 64 sequences are dealt to the ranks by cache pages, the packed long-context case
+benchmark's 64 sequences are dealt to the ranks by cache pages (with as many partial slots per
+sequence as `mla.decode_splits` asks for that share), the packed long-context case
 runs 16 heads per GPU, and a small head-sharded problem is gathered over NCCL and compared with
 the CPU oracle on rank 0.  After the timed regions rank 0 also compares slices of the timed
 outputs themselves with the oracle; the line carries the outcome as `verified`.
